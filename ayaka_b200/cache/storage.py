@@ -43,8 +43,8 @@ class CachePlan:
 
     def bytes_per_page(self, group: int, itemsize: int, page_size: int) -> int:
         need = self.groups[group]
-        return (2 * self.slots_per_group[group] * need.num_kv_heads * page_size
-                * need.head_dim * itemsize)
+        return ((2 if need.values else 1) * self.slots_per_group[group] * need.num_kv_heads
+                * page_size * need.head_dim * itemsize)
 
     def bytes_per_token(self, itemsize: int) -> int:
         """Key and value bytes one cached token takes over all groups (windows ignored)."""
@@ -94,11 +94,13 @@ class CacheStorage:
         self.plan = plan
         self.page_size = page_size
         self.keys: list[torch.Tensor] = []
-        self.values: list[torch.Tensor] = []
+        self.values: list[torch.Tensor | None] = []
         for need, slots, pages in zip(plan.groups, plan.slots_per_group, num_pages):
             shape = (slots, pages, need.num_kv_heads, page_size, need.head_dim)
             self.keys.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.values.append(torch.zeros(shape, dtype=dtype, device=device))
+            # a group of latent rows keeps one tensor: its rows are keys and values at once
+            self.values.append(torch.zeros(shape, dtype=dtype, device=device)
+                               if need.values else None)
         if poison:
             self.poison()
         self.states: list[torch.Tensor | None] = [
@@ -109,7 +111,8 @@ class CacheStorage:
     def poison(self) -> None:
         """Fill every page with NaN (tests: a slot read before it is written then shows)."""
         for tensor in (*self.keys, *self.values):
-            tensor.fill_(float("nan"))
+            if tensor is not None:
+                tensor.fill_(float("nan"))
 
     def layer_caches(self) -> list[LayerCache]:
         """One :class:`LayerCache` per run of the order."""
@@ -119,7 +122,9 @@ class CacheStorage:
                 out.append(LayerCache(None, None, None, False, self.states[index]))
             else:
                 slot = self.plan.run_slot[index]
-                out.append(LayerCache(group, self.keys[group][slot], self.values[group][slot],
+                values = self.values[group]
+                out.append(LayerCache(group, self.keys[group][slot],
+                                      None if values is None else values[slot],
                                       self.plan.run_writes[index], self.states[index]))
         return out
 
@@ -131,5 +136,6 @@ class CacheStorage:
                 state[rows] = 0
 
     def nbytes(self) -> int:
-        total = sum(t.numel() * t.element_size() for t in (*self.keys, *self.values))
+        total = sum(t.numel() * t.element_size() for t in (*self.keys, *self.values)
+                    if t is not None)
         return total + sum(t.numel() * t.element_size() for t in self.states if t is not None)

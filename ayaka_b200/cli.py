@@ -38,7 +38,7 @@ def say(text: str) -> None:
 
 
 def _parser() -> argparse.ArgumentParser:
-    parser = argparse.ArgumentParser(prog=PROG, description="GPT-2 inference on one B200.")
+    parser = argparse.ArgumentParser(prog=PROG, description="Decoder inference on one B200.")
     commands = parser.add_subparsers(dest="command", metavar="command")
     run = commands.add_parser("run", help="generate token ids for a prompt and print them")
     run.add_argument("model", help="a local model folder (config.json, model.safetensors)")
@@ -128,8 +128,9 @@ def _run(args: argparse.Namespace) -> int:
     with LLM.from_config(config) as llm:
         if not args.quiet:
             spec = llm.core.model.spec
-            say(f"{Path(args.model).name}: {len(spec.layers)} layers, width {spec.hidden_size}, "
-                f"{config.dtype}, {llm.core.manager.pools[0].num_usable} cache pages of "
+            pools = llm.core.manager.pools
+            say(f"{Path(args.model).name}: {len(spec.order)} layers, width {spec.hidden_size}, "
+                f"{config.dtype}, {pools[0].num_usable if pools else 0} cache pages of "
                 f"{config.block_size}")
         first = True
         for output in llm.stream(tuple(prompt), params):

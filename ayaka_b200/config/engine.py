@@ -37,6 +37,9 @@ class EngineConfig:
             else sizes it.
         kv_reserve_tokens: tokens the cache must hold in total; ``None`` means
             ``max_running`` full contexts (bounded by ``memory_ratio``).
+        max_context: longest sequence (prompt plus generated tokens) a request may reach;
+            ``None``: the model's own limit, and for a model without one what the cache
+            pool holds.
         max_running: most requests live at once (rows of the block table).
         max_tokens_per_step: token budget of one step.
         max_waiting: longest queue of requests not yet admitted.
@@ -53,6 +56,7 @@ class EngineConfig:
     num_blocks: int | None = None
     memory_ratio: float = 0.90
     kv_reserve_tokens: int | None = None
+    max_context: int | None = None
     max_running: int = 8
     max_tokens_per_step: int = 2048
     max_waiting: int = 1024
@@ -79,6 +83,9 @@ class EngineConfig:
         if self.kv_reserve_tokens is not None and (
                 type(self.kv_reserve_tokens) is not int or self.kv_reserve_tokens < 1):
             raise ConfigError("engine.kv_reserve_tokens", "INVALID_RANGE", "must be >= 1")
+        if self.max_context is not None and (
+                type(self.max_context) is not int or self.max_context < 1):
+            raise ConfigError("engine.max_context", "INVALID_RANGE", "must be >= 1")
         if self.num_blocks is not None:
             if type(self.num_blocks) is not int or self.num_blocks < 2:
                 raise ConfigError("engine.num_blocks", "NUM_BLOCKS_TOO_SMALL",

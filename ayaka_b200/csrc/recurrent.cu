@@ -1,0 +1,392 @@
+// Layers with a running per-request state instead of cached keys: the short causal
+// convolution and the selective state-space recurrence of a Mamba-2 layer, and the matrix
+// memory of an mLSTM layer. A step brings each request's next rows (a prompt portion or one
+// token); the state a request left behind is read from its slot, carried over the rows in
+// order, and written back. Everything here is fp32.
+//
+// Both recurrences have the shape S_t = a_t S_(t-1) + b_t k_t v_t^T, y_t = S_t^T q_t with S
+// [n x p] per head, so the p columns of S never mix: a CTA owns one (head, request, tile of
+// SCAN_COLS columns); a column's n entries are spread over SCAN_LANES neighbouring lanes
+// (entry n on lane n % SCAN_LANES), which add up their shares of y with three shuffles. The
+// rows are taken in chunks: the chunk's inputs are brought to shared memory by all threads
+// (and the gates turned into factors there, one thread per row), then every thread walks the
+// chunk row by row.
+#include "common.cuh"
+
+namespace ayk {
+
+constexpr int SCAN_COLS = 16;   // columns of the state per CTA
+constexpr int SCAN_LANES = 8;   // lanes that share a column
+constexpr int SCAN_THREADS = SCAN_COLS * SCAN_LANES;
+constexpr int CONV_MAX_TAPS = 16;
+
+__device__ __forceinline__ float group_sum8(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
+__device__ __forceinline__ float softplus_f(float z) {  // log(1 + e^z), exact for any z
+  return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+}
+__device__ __forceinline__ float log_sigmoid_f(float z) {  // -log(1 + e^-z)
+  return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+}
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+
+// ---------------------------------------------------------------------------------------------
+// out[r][c] = silu(bias[c] + sum_l w[c][taps - 1 - l] * u[t - l][c]), l = 0 .. taps - 1, where
+// u[t - l] is a row of this step if the request has it in this step, else one of the last
+// taps - 1 inputs kept in the request's state (conv[k] = the input taps - 1 - k rows before the
+// step's first), zeros before the sequence's start.
+__global__ void causal_conv_silu_kernel(const float* __restrict__ in, int ld_in,
+                                        const float* __restrict__ w,
+                                        const float* __restrict__ bias,
+                                        const float* __restrict__ state, long long state_stride,
+                                        const int* __restrict__ request_of_row,
+                                        const int* __restrict__ row_start,
+                                        const int* __restrict__ state_slot,
+                                        float* __restrict__ out, int ld_out, int channels,
+                                        int taps) {
+  pdl_launch_dependents();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x, r = blockIdx.x;
+  const int b = request_of_row[r];
+  if (c >= channels || b < 0) return;
+  const int j = r - row_start[b];
+  const float* kept = state + (size_t)state_slot[b] * state_stride;
+  float wv[CONV_MAX_TAPS];
+#pragma unroll
+  for (int l = 0; l < CONV_MAX_TAPS; ++l) wv[l] = l < taps ? w[(size_t)c * taps + taps - 1 - l] : 0.f;
+  float acc = bias != nullptr ? bias[c] : 0.f;
+  pdl_wait_for(in, kept);
+#pragma unroll
+  for (int l = 0; l < CONV_MAX_TAPS; ++l) {
+    if (l < taps) {
+      const float u = j - l >= 0 ? in[(size_t)(r - l) * ld_in + c]
+                                 : kept[(size_t)(taps - 1 + j - l) * channels + c];
+      acc = fmaf(wv[l], u, acc);
+    }
+  }
+  out[(size_t)r * ld_out + c] = silu_f(acc);
+}
+
+// After the convolution has read it, the kept inputs move on: conv[k] <- the input
+// taps - 1 - k rows before the row that follows this step.
+__global__ void conv_state_update_kernel(const float* __restrict__ in, int ld_in,
+                                         float* __restrict__ state, long long state_stride,
+                                         const int* __restrict__ row_start,
+                                         const int* __restrict__ state_slot, int channels,
+                                         int taps) {
+  pdl_launch_dependents();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (c >= channels) return;
+  const int r0 = row_start[b], rows = row_start[b + 1] - r0;
+  float* kept = state + (size_t)state_slot[b] * state_stride;
+  pdl_wait_for(in, kept);
+  float next[CONV_MAX_TAPS];
+#pragma unroll
+  for (int k = 0; k < CONV_MAX_TAPS - 1; ++k) {
+    if (k < taps - 1) {
+      const int j = rows - (taps - 1) + k;  // index among the step's rows
+      next[k] = j >= 0 ? in[(size_t)(r0 + j) * ld_in + c] : kept[(size_t)(k + rows) * channels + c];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < CONV_MAX_TAPS - 1; ++k) {
+    if (k < taps - 1) kept[(size_t)k * channels + c] = next[k];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Mamba-2: per head h (group g = h / (heads / groups)), dt = softplus(dt_raw + dt_bias),
+//   S <- exp(-exp(A_log) dt) S + dt B x^T,   y = S^T C + D x,    S: [N x P].
+// xbc rows: [ x: heads x P | B: groups x N | C: groups x N ] (after convolution and silu).
+// State of a request's slot: S as [heads][N][P] from `state`.
+template <int RN>  // entries of a column per lane: N <= SCAN_LANES * RN
+__global__ void __launch_bounds__(SCAN_THREADS)
+mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __restrict__ dt_raw,
+                   int ld_dt, const float* __restrict__ dt_bias,
+                   const float* __restrict__ a_log, const float* __restrict__ skip,
+                   float* __restrict__ state, long long state_stride,
+                   const int* __restrict__ row_start, const int* __restrict__ state_slot,
+                   float* __restrict__ y, int ld_y, int heads, int groups, int N, int P,
+                   int chunk) {
+  extern __shared__ float scan_smem[];
+  float* b_s = scan_smem;                 // [chunk][N]
+  float* c_s = b_s + (size_t)chunk * N;   // [chunk][N]
+  float* x_s = c_s + (size_t)chunk * N;   // [chunk][SCAN_COLS]
+  float* dt_s = x_s + chunk * SCAN_COLS;  // [chunk]
+  float* decay_s = dt_s + chunk;          // [chunk]
+  pdl_launch_dependents();
+  const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * SCAN_COLS;
+  const int col = threadIdx.x / SCAN_LANES, part = threadIdx.x % SCAN_LANES;
+  const int p = p0 + col;
+  const bool live = p < P;
+  const int g = h / (heads / groups), inner = heads * P;
+  const int r0 = row_start[b], rows = row_start[b + 1] - r0;
+  const float rate = -expf(a_log[h]), bias = dt_bias[h], d_skip = skip != nullptr ? skip[h] : 0.f;
+  float* mine = state + (size_t)state_slot[b] * state_stride + (size_t)h * N * P;
+  pdl_wait_for(xbc, dt_raw, mine);
+  float s[RN];
+#pragma unroll
+  for (int k = 0; k < RN; ++k) {
+    const int n = part + SCAN_LANES * k;
+    s[k] = (live && n < N) ? mine[(size_t)n * P + p] : 0.f;
+  }
+  for (int t0 = 0; t0 < rows; t0 += chunk) {
+    const int count = min(chunk, rows - t0);
+    __syncthreads();  // the chunk before has been walked
+    const float* first = xbc + (size_t)(r0 + t0) * ld_xbc;
+    for (int idx = threadIdx.x; idx < count * N; idx += SCAN_THREADS) {
+      const int i = idx / N, n = idx % N;
+      const float* row = first + (size_t)i * ld_xbc + inner + g * N;
+      b_s[idx] = row[n];
+      c_s[idx] = row[groups * N + n];
+    }
+    for (int idx = threadIdx.x; idx < count * SCAN_COLS; idx += SCAN_THREADS) {
+      const int i = idx / SCAN_COLS, cc = idx % SCAN_COLS;
+      x_s[idx] = p0 + cc < P ? first[(size_t)i * ld_xbc + h * P + p0 + cc] : 0.f;
+    }
+    for (int i = threadIdx.x; i < count; i += SCAN_THREADS) {
+      const float dt = softplus_f(dt_raw[(size_t)(r0 + t0 + i) * ld_dt + h] + bias);
+      dt_s[i] = dt;
+      decay_s[i] = expf(rate * dt);
+    }
+    __syncthreads();
+    for (int i = 0; i < count; ++i) {
+      const float decay = decay_s[i], xv = x_s[i * SCAN_COLS + col];
+      const float push = dt_s[i] * xv;
+      const float* bi = b_s + (size_t)i * N;
+      const float* ci = c_s + (size_t)i * N;
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < RN; ++k) {
+        const int n = part + SCAN_LANES * k;
+        if (n < N) {
+          s[k] = fmaf(decay, s[k], push * bi[n]);
+          acc = fmaf(s[k], ci[n], acc);
+        }
+      }
+      acc = group_sum8(acc);
+      if (part == 0 && live) y[(size_t)(r0 + t0 + i) * ld_y + h * P + p] = acc + d_skip * xv;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < RN; ++k) {
+    const int n = part + SCAN_LANES * k;
+    if (live && n < N) mine[(size_t)n * P + p] = s[k];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// mLSTM: per head, with log gates i = cap tanh((i_raw + b_i) / cap) and
+// f = logsigmoid(cap tanh((f_raw + b_f) / cap)) and a running maximum m (0 at the start):
+//   m' = max(f + m, i);  keep = e^(f + m - m'), take = e^(i - m');
+//   S <- keep S + take k v^T;  n <- keep n + take k;
+//   out = S^T q / (max(|n . q|, e^(-m')) + 1e-6),   q already times dim^(-1/2).
+// proj rows: [ q: H x dim | k: H x dim | v: H x P | (gate, not read here) | i_raw: H | f_raw: H ]
+// at the given offsets. State of a slot: S [H][dim][P]; then, once per tile of SCAN_COLS
+// columns so that no CTA reads what another writes, n [H][tiles][dim] and m [H][tiles].
+template <int RN>
+__global__ void __launch_bounds__(SCAN_THREADS)
+mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int v_offset,
+                  int i_offset, int f_offset, const float* __restrict__ gate_bias, float cap,
+                  float* __restrict__ state, long long state_stride,
+                  const int* __restrict__ row_start, const int* __restrict__ state_slot,
+                  float* __restrict__ out, int ld_out, int heads, int dim, int P, int chunk) {
+  extern __shared__ float scan_smem[];
+  float* q_s = scan_smem;                   // [chunk][dim]
+  float* k_s = q_s + (size_t)chunk * dim;   // [chunk][dim]
+  float* v_s = k_s + (size_t)chunk * dim;   // [chunk][SCAN_COLS]
+  float* keep_s = v_s + chunk * SCAN_COLS;  // [chunk]: log gate f, then the factor
+  float* take_s = keep_s + chunk;           // [chunk]: log gate i, then the factor
+  float* floor_s = take_s + chunk;          // [chunk]: e^(-m')
+  __shared__ float m_run;
+  pdl_launch_dependents();
+  const int h = blockIdx.x, b = blockIdx.y, tile = blockIdx.z, tiles = gridDim.z;
+  const int p0 = tile * SCAN_COLS;
+  const int col = threadIdx.x / SCAN_LANES, part = threadIdx.x % SCAN_LANES;
+  const int p = p0 + col;
+  const bool live = p < P;
+  const int r0 = row_start[b], rows = row_start[b + 1] - r0;
+  const float q_scale = 1.f / sqrtf((float)dim);
+  const float bias_i = gate_bias != nullptr ? gate_bias[h] : 0.f;
+  const float bias_f = gate_bias != nullptr ? gate_bias[heads + h] : 0.f;
+  float* slot = state + (size_t)state_slot[b] * state_stride;
+  float* mine = slot + (size_t)h * dim * P;
+  float* norm_mine = slot + (size_t)heads * dim * P + ((size_t)h * tiles + tile) * dim;
+  float* max_mine = slot + (size_t)heads * dim * P + (size_t)heads * tiles * dim + h * tiles + tile;
+  pdl_wait_for(proj, mine, norm_mine, max_mine);
+  float s[RN], nrm[RN];
+#pragma unroll
+  for (int k = 0; k < RN; ++k) {
+    const int n = part + SCAN_LANES * k;
+    s[k] = (live && n < dim) ? mine[(size_t)n * P + p] : 0.f;
+    nrm[k] = n < dim ? norm_mine[n] : 0.f;
+  }
+  if (threadIdx.x == 0) m_run = *max_mine;
+  for (int t0 = 0; t0 < rows; t0 += chunk) {
+    const int count = min(chunk, rows - t0);
+    __syncthreads();
+    const float* first = proj + (size_t)(r0 + t0) * ld_proj;
+    for (int idx = threadIdx.x; idx < count * dim; idx += SCAN_THREADS) {
+      const int i = idx / dim, n = idx % dim;
+      const float* row = first + (size_t)i * ld_proj + h * dim;
+      q_s[idx] = row[n] * q_scale;
+      k_s[idx] = row[k_offset + n];
+    }
+    for (int idx = threadIdx.x; idx < count * SCAN_COLS; idx += SCAN_THREADS) {
+      const int i = idx / SCAN_COLS, cc = idx % SCAN_COLS;
+      v_s[idx] = p0 + cc < P ? first[(size_t)i * ld_proj + v_offset + h * P + p0 + cc] : 0.f;
+    }
+    for (int i = threadIdx.x; i < count; i += SCAN_THREADS) {
+      const float* row = first + (size_t)i * ld_proj;
+      take_s[i] = cap * tanhf((row[i_offset + h] + bias_i) / cap);
+      keep_s[i] = log_sigmoid_f(cap * tanhf((row[f_offset + h] + bias_f) / cap));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {  // the scalar recurrence of the maximum, in row order
+      float m = m_run;
+      for (int i = 0; i < count; ++i) {
+        const float f = keep_s[i], ig = take_s[i];
+        const float m_new = fmaxf(f + m, ig);
+        keep_s[i] = expf(f + m - m_new);
+        take_s[i] = expf(ig - m_new);
+        floor_s[i] = expf(-m_new);
+        m = m_new;
+      }
+      m_run = m;
+    }
+    __syncthreads();
+    for (int i = 0; i < count; ++i) {
+      const float keep = keep_s[i], take = take_s[i];
+      const float tv = take * v_s[i * SCAN_COLS + col];
+      const float* qi = q_s + (size_t)i * dim;
+      const float* ki = k_s + (size_t)i * dim;
+      float acc = 0.f, dot = 0.f;
+#pragma unroll
+      for (int k = 0; k < RN; ++k) {
+        const int n = part + SCAN_LANES * k;
+        if (n < dim) {
+          const float kk = ki[n], qq = qi[n];
+          s[k] = fmaf(keep, s[k], tv * kk);
+          nrm[k] = fmaf(keep, nrm[k], take * kk);
+          acc = fmaf(s[k], qq, acc);
+          dot = fmaf(nrm[k], qq, dot);
+        }
+      }
+      acc = group_sum8(acc);
+      dot = group_sum8(dot);
+      if (part == 0 && live) {
+        out[(size_t)(r0 + t0 + i) * ld_out + h * P + p] =
+            acc / (fmaxf(fabsf(dot), floor_s[i]) + 1e-6f);
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < RN; ++k) {
+    const int n = part + SCAN_LANES * k;
+    if (live && n < dim) mine[(size_t)n * P + p] = s[k];
+    if (col == 0 && n < dim) norm_mine[n] = nrm[k];
+  }
+  if (threadIdx.x == 0) *max_mine = m_run;
+}
+
+inline int scan_chunk(int n) { return n <= 128 ? 32 : 16; }
+
+}  // namespace ayk
+
+AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
+
+AYK_API int ayk_scan_columns() { return ayk::SCAN_COLS; }
+
+// `in`: the step's rows, column 0 = channel 0 (a column range of the projection output);
+// `state`: the first of (taps - 1) x channels kept inputs of slot 0; slots are state_stride
+// floats apart. The convolution, then the update of the kept inputs: two launches.
+AYK_API int ayk_causal_conv_silu(const float* in, int ld_in, const float* w, const float* bias,
+                                 float* state, long long state_stride, const int* request_of_row,
+                                 const int* row_start, const int* state_slot, float* out,
+                                 int ld_out, int rows, int requests, int channels, int taps,
+                                 void* stream) {
+  using namespace ayk;
+  if (rows == 0 || channels == 0) return AYK_OK;
+  if (rows < 0 || requests < 1 || channels < 0 || taps < 1 || in == nullptr || w == nullptr ||
+      state == nullptr || request_of_row == nullptr || row_start == nullptr ||
+      state_slot == nullptr || out == nullptr || ld_in < channels || ld_out < channels ||
+      requests > 65535) {
+    return AYK_BAD_ARGUMENT;
+  }
+  const int threads = 128, tiles = (channels + threads - 1) / threads;
+  if (taps > CONV_MAX_TAPS || tiles > 65535) return AYK_TOO_LARGE;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int status = launch_kernel(causal_conv_silu_kernel, dim3(rows, tiles), dim3(threads), 0,
+                                   s, 1, in, ld_in, w, bias, (const float*)state, state_stride,
+                                   request_of_row, row_start, state_slot, out, ld_out, channels,
+                                   taps);
+  if (status != AYK_OK || taps == 1) return status;
+  return launch_kernel(conv_state_update_kernel, dim3(tiles, requests), dim3(threads), 0, s, 1,
+                       in, ld_in, state, state_stride, row_start, state_slot, channels, taps);
+}
+
+AYK_API int ayk_mamba2_scan(const float* xbc, int ld_xbc, const float* dt_raw, int ld_dt,
+                            const float* dt_bias, const float* a_log, const float* skip,
+                            float* state, long long state_stride, const int* row_start,
+                            const int* state_slot, float* y, int ld_y, int requests, int heads,
+                            int groups, int N, int P, void* stream) {
+  using namespace ayk;
+  if (requests == 0) return AYK_OK;
+  if (requests < 0 || heads < 1 || groups < 1 || heads % groups || N < 1 || P < 1 ||
+      xbc == nullptr || dt_raw == nullptr || dt_bias == nullptr || a_log == nullptr ||
+      state == nullptr || row_start == nullptr || state_slot == nullptr || y == nullptr ||
+      ld_xbc < heads * P + 2 * groups * N || ld_dt < heads || ld_y < heads * P ||
+      requests > 65535) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (N > SCAN_LANES * 32 || (P + SCAN_COLS - 1) / SCAN_COLS > 65535) return AYK_TOO_LARGE;
+  const int chunk = scan_chunk(N);
+  const size_t smem = ((size_t)chunk * (2 * N + SCAN_COLS + 2)) * sizeof(float);
+  const dim3 grid(heads, requests, (P + SCAN_COLS - 1) / SCAN_COLS);
+#define AYK_MAMBA(RN)                                                                          \
+  return launch_kernel(mamba2_scan_kernel<RN>, grid, dim3(SCAN_THREADS), smem,                 \
+                       (cudaStream_t)stream, 1, xbc, ld_xbc, dt_raw, ld_dt, dt_bias, a_log,    \
+                       skip, state, state_stride, row_start, state_slot, y, ld_y, heads,       \
+                       groups, N, P, chunk)
+  if (N <= SCAN_LANES * 2) AYK_MAMBA(2);
+  if (N <= SCAN_LANES * 4) AYK_MAMBA(4);
+  if (N <= SCAN_LANES * 8) AYK_MAMBA(8);
+  if (N <= SCAN_LANES * 16) AYK_MAMBA(16);
+  AYK_MAMBA(32);
+#undef AYK_MAMBA
+}
+
+AYK_API int ayk_mlstm_scan(const float* proj, int ld_proj, int k_offset, int v_offset,
+                           int i_offset, int f_offset, const float* gate_bias, float cap,
+                           float* state, long long state_stride, const int* row_start,
+                           const int* state_slot, float* out, int ld_out, int requests, int heads,
+                           int dim, int P, void* stream) {
+  using namespace ayk;
+  if (requests == 0) return AYK_OK;
+  const int tiles = (P + SCAN_COLS - 1) / SCAN_COLS;
+  if (requests < 0 || heads < 1 || dim < 1 || P < 1 || proj == nullptr || state == nullptr ||
+      row_start == nullptr || state_slot == nullptr || out == nullptr || !(cap > 0.f) ||
+      ld_out < heads * P || requests > 65535 ||
+      state_stride < (long long)heads * dim * P + (long long)heads * tiles * (dim + 1)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (dim > SCAN_LANES * 32 || tiles > 65535) return AYK_TOO_LARGE;
+  const int chunk = scan_chunk(dim);
+  const size_t smem = ((size_t)chunk * (2 * dim + SCAN_COLS + 3)) * sizeof(float);
+  const dim3 grid(heads, requests, tiles);
+#define AYK_MLSTM(RN)                                                                          \
+  return launch_kernel(mlstm_scan_kernel<RN>, grid, dim3(SCAN_THREADS), smem,                  \
+                       (cudaStream_t)stream, 1, proj, ld_proj, k_offset, v_offset, i_offset,   \
+                       f_offset, gate_bias, cap, state, state_stride, row_start, state_slot,   \
+                       out, ld_out, heads, dim, P, chunk)
+  if (dim <= SCAN_LANES * 2) AYK_MLSTM(2);
+  if (dim <= SCAN_LANES * 4) AYK_MLSTM(4);
+  if (dim <= SCAN_LANES * 8) AYK_MLSTM(8);
+  if (dim <= SCAN_LANES * 16) AYK_MLSTM(16);
+  AYK_MLSTM(32);
+#undef AYK_MLSTM
+}

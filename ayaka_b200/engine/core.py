@@ -20,6 +20,12 @@ __all__ = ["EngineCore"]
 
 _DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
+#: A model whose ``max_positions`` is at least this has no limit of its own (no position
+#: table); the engine then bounds a sequence by ``EngineConfig.max_context`` or by its cache.
+UNBOUNDED_CONTEXT = 1 << 30
+#: tokens of cache per running request when such a model comes with no other sizing
+DEFAULT_CONTEXT = 8192
+
 
 class EngineCore:
     """A loaded model with its cache and step function on one CUDA device.
@@ -31,7 +37,8 @@ class EngineCore:
 
     def __init__(self, model: DecoderModel, model_config: object, *, dtype: str,
                  device: torch.device, block_size: int, num_blocks: int, max_running: int,
-                 max_tokens_per_step: int, poison_cache: bool = False) -> None:
+                 max_tokens_per_step: int, poison_cache: bool = False,
+                 max_context: int | None = None) -> None:
         self.model = model
         self.model_config = model_config
         self.dtype = dtype
@@ -39,12 +46,18 @@ class EngineCore:
         spec = model.spec
         self.cache_plan = plan_cache(spec.order, model.needs())
         groups = len(self.cache_plan.groups)
-        pages_per_request = -(-spec.max_positions // block_size)
+        #: the longest sequence a request may reach here: the model's limit, the configured
+        #: one, and for a model that has none (no table of positions) what the pool holds
+        self.max_positions = min(spec.max_positions, max_context or spec.max_positions)
+        if self.max_positions >= UNBOUNDED_CONTEXT:
+            self.max_positions = (num_blocks - 1) * block_size
+        pages_per_request = -(-self.max_positions // block_size)
         self.manager = CacheManager(list(self.cache_plan.groups), [num_blocks] * groups,
                                     block_size, max_running, pages_per_request)
         self.storage = CacheStorage(self.cache_plan, [num_blocks] * groups, block_size,
                                     max_running, _DTYPES[dtype], device, poison=poison_cache)
-        self.runner = ModelRunner(model, self.manager, self.storage, max_tokens_per_step, device)
+        self.runner = ModelRunner(model, self.manager, self.storage, max_tokens_per_step, device,
+                                  max_positions=self.max_positions)
 
     @classmethod
     def from_config(cls, config: EngineConfig,
@@ -67,7 +80,10 @@ class EngineCore:
         itemsize = 4 if config.dtype == "float32" else 2
         num_blocks = config.num_blocks
         if num_blocks is None:
-            wanted_tokens = config.kv_reserve_tokens or config.max_running * spec.max_positions
+            context = min(spec.max_positions, config.max_context or spec.max_positions)
+            if context >= UNBOUNDED_CONTEXT:
+                context = DEFAULT_CONTEXT
+            wanted_tokens = config.kv_reserve_tokens or config.max_running * context
             num_blocks = -(-wanted_tokens // config.block_size) + config.max_running + 1
             per_page = sum(plan.bytes_per_page(g, itemsize, config.block_size)
                            for g in range(len(plan.groups)))
@@ -83,7 +99,8 @@ class EngineCore:
         return cls(model, model_config, dtype=config.dtype, device=device,
                    block_size=config.block_size, num_blocks=num_blocks,
                    max_running=config.max_running,
-                   max_tokens_per_step=config.max_tokens_per_step, poison_cache=poison_cache)
+                   max_tokens_per_step=config.max_tokens_per_step, poison_cache=poison_cache,
+                   max_context=config.max_context)
 
     # ------------------------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:

@@ -77,7 +77,7 @@ class _Bucket:
                               view(o_slots, size), manager.page_size)
                     for o_slots, o_table in self.o_groups],
             workspace=core.runner.workspace, bad_index=core.runner._bad_index,
-            max_kv_len=core.model.spec.max_positions, decode_only=True)
+            max_kv_len=core.max_positions, decode_only=True)
         self.want_rows = view(self.o_want, size)
         self.argmax_scratch = torch.zeros(2 * size * ops.ARGMAX_PARTS, device=core.device)
         # one graph for steps whose rows are all greedy (argmax), one for any other step

@@ -42,7 +42,8 @@ class LLM:
         self.scheduler = Scheduler(
             core.manager, max_running=config.max_running,
             max_tokens_per_step=config.max_tokens_per_step, max_waiting=config.max_waiting,
-            max_positions=spec.max_positions, eos_token_id=spec.eos_token_id)
+            max_positions=getattr(core, "max_positions", spec.max_positions),
+            eos_token_id=spec.eos_token_id)
         self.sampler = Sampler(max(config.max_running, 1), core.device, core.runner.flags)
         self._counter = 0
         self._pending: dict[str, deque[RequestEvent]] = {}

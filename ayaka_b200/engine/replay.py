@@ -46,6 +46,7 @@ def main(argv: list[str] | None = None) -> int:
     try:
         config = EngineConfig(
             model=args.model, dtype=args.dtype, block_size=page, num_blocks=num_blocks,
+            max_context=max(args.max_tokens, page),
             max_running=max(1, min(args.max_running, num_blocks - 1)),
             max_tokens_per_step=max(args.max_tokens_per_step or args.max_tokens, page))
         core = EngineCore.from_config(config)

@@ -53,8 +53,10 @@ class ModelRunner:
     """Owns the workspace and the metadata buffers; turns entries into logits."""
 
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: CacheStorage,
-                 max_rows: int, device: torch.device) -> None:
+                 max_rows: int, device: torch.device, max_positions: int | None = None) -> None:
         self.model = model
+        self.max_positions = model.spec.max_positions if max_positions is None \
+            else max_positions
         self.manager = manager
         self.storage = storage
         self.max_rows = max_rows
@@ -118,10 +120,10 @@ class ModelRunner:
             if count < 1:
                 raise InvalidRequestError(f"request {entry.request_id!r} brings no token")
             start = manager.committed(entry.request_id)
-            if start + count > spec.max_positions:
+            if start + count > self.max_positions:
                 raise InvalidRequestError(
                     f"request {entry.request_id!r} would reach position {start + count - 1}, "
-                    f"past the model's {spec.max_positions} positions")
+                    f"past the {self.max_positions} positions a sequence may have here")
             rows.append(count)
             starts.append(start)
             table_rows.append(manager.row(entry.request_id))

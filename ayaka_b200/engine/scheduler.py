@@ -164,7 +164,8 @@ class Scheduler:
         held = 0
         if request.request_id in manager:
             held = -(-request.computed // page) * page - request.computed
-        free = min(manager.num_free_pages(group) for group in range(len(manager.needs)))
+        free = min((manager.num_free_pages(group) for group in range(len(manager.needs))),
+                   default=size)  # (a model without cached keys holds no page)
         shrunk = min(size, held + free * page)
         if 1 <= shrunk < size and manager.allocate(request.request_id, shrunk):
             return shrunk

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import contextlib
 from collections.abc import Iterator
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -23,9 +23,13 @@ __all__ = [
     "attention",
     "attention_decode",
     "attention_prefill",
+    "causal_conv_silu",
     "decode_splits",
     "embed_rows",
+    "head_linear",
     "kv_store",
+    "latent_attention",
+    "latent_prepare",
     "launch_count",
     "leaving_out",
     "layer_norm",
@@ -33,7 +37,13 @@ __all__ = [
     "linear_normed",
     "logits_adjust",
     "logits_scale_cap",
+    "mamba2_scan",
+    "mlstm_scan",
+    "rms_norm",
+    "rope",
+    "rope_frequencies",
     "sample",
+    "scan_state_floats",
     "set_decode_tensor_cores",
     "set_pdl",
     "sm_count",
@@ -75,7 +85,9 @@ def leaving_out(*classes: str) -> Iterator[None]:
 
 
 _TIMED = ("embed_rows", "layer_norm", "linear", "linear_kv", "kv_store", "attention",
-          "attention_prefill", "attention_decode", "argmax", "sample")
+          "attention_prefill", "attention_decode", "argmax", "sample", "rms_norm", "rope",
+          "latent_prepare", "head_linear", "latent_attention", "causal_conv_silu", "mamba2_scan",
+          "mlstm_scan")
 
 
 @contextlib.contextmanager
@@ -679,4 +691,323 @@ def logits_adjust(logits: torch.Tensor, desc: torch.Tensor, num_rows: int,
     status = library("sampling").ayk_logits_adjust(
         _ptr(logits), c_int(logits.stride(0)), c_int(logits.shape[1]), _ptr(desc),
         c_int(num_rows), _ptr(mask_scratch), _stream())
+    check(status, op)
+
+
+# ---- norms by the root mean square, rotations ---------------------------------------------
+
+GATES = {"none": 0, "silu_before": 1, "sigmoid_after": 2}
+ROPE_LAYOUTS = {"neighbours": 0, "halves": 1}
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *,
+             weight_offset: float = 0.0, groups: int = 1, rows: torch.Tensor | None = None,
+             count: int | None = None, gate: torch.Tensor | None = None,
+             gate_mode: str = "none") -> None:
+    """``out = x * rsqrt(mean(x^2) + eps) * (weight_offset + weight)`` over fp32 rows, the mean
+    over each of ``groups`` equal parts of a row on its own; ``out`` float32 or bfloat16.
+
+    With ``rows`` (int32), output row ``i`` normalises ``x[rows[i]]``. With ``gate`` (float32,
+    laid out like ``x``): ``gate_mode="silu_before"`` multiplies ``x`` by ``silu(gate)`` before
+    the norm, ``"sigmoid_after"`` multiplies the result by ``sigmoid(gate)``.
+    """
+    op = "rms_norm"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "x", x, torch.float32, 2)
+    _need(op, "weight", weight, torch.float32, 1)
+    _need(op, "out", out, ndim=2)
+    if out.dtype not in _TYPE:
+        raise BackendError(f"{op}: out must be float32 or bfloat16, got {out.dtype}")
+    width = weight.shape[0]
+    if x.shape[1] != width or out.shape[1] != width or groups < 1 or width % groups:
+        raise BackendError(f"{op}: widths differ or {groups} groups do not divide {width}")
+    if gate_mode not in GATES or (gate is None) != (gate_mode == "none"):
+        raise BackendError(f"{op}: gate and gate_mode {gate_mode!r} do not go together")
+    if gate is not None:
+        _need(op, "gate", gate, torch.float32, 2)
+        if gate.shape[1] != width or gate.shape[0] < x.shape[0]:
+            raise BackendError(f"{op}: the gate does not match x")
+    if rows is not None:
+        _need(op, "rows", rows, torch.int32, 1)
+    n = count if count is not None else (rows.shape[0] if rows is not None else x.shape[0])
+    if n > out.shape[0] or (rows is None and n > x.shape[0]) or \
+            (rows is not None and n > rows.shape[0]):
+        raise BackendError(f"{op}: {n} rows do not fit the tensors")
+    status = library("rms_norm").ayk_rms_norm(
+        _ptr(x), c_int(x.stride(0)), _ptr(rows), _ptr(weight), c_float(weight_offset),
+        c_float(eps), c_int(groups), _ptr(gate), c_int(0 if gate is None else gate.stride(0)),
+        c_int(GATES[gate_mode]), _ptr(out), c_int(out.stride(0)), c_int(n), c_int(width),
+        c_int(_TYPE[out.dtype]), _stream())
+    check(status, op)
+
+
+def rope_frequencies(dims: int, base: float, device: torch.device) -> torch.Tensor:
+    """``f_i = base^(-2i / dims)`` for the ``dims / 2`` pairs, as float64 on ``device`` (the
+    kernels form ``position * f_i`` and its sine and cosine in double precision)."""
+    values = [float(base) ** (-2.0 * i / dims) for i in range(dims // 2)]
+    return torch.tensor(values, dtype=torch.float64, device=device)
+
+
+def rope(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, *, heads: int,
+         head_stride: int, offset: int = 0, layout: str = "neighbours",
+         rows: int | None = None) -> None:
+    """Rotary position encoding in place: in each of the ``heads`` stretches of
+    ``head_stride`` values of a row, the ``2 * len(freq)`` entries from ``offset`` on are
+    rotated by ``positions[row] * freq[i]``: pair ``i`` is entries ``(2i, 2i+1)``
+    (``"neighbours"``) or ``(i, i + dims/2)`` (``"halves"``)."""
+    op = "rope"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "x", x, ndim=2)
+    _need(op, "positions", positions, torch.int32, 1)
+    _need(op, "freq", freq, torch.float64, 1)
+    if x.dtype not in _TYPE or layout not in ROPE_LAYOUTS:
+        raise BackendError(f"{op}: float32 or bfloat16 rows and a known layout only")
+    n = x.shape[0] if rows is None else rows
+    if n > x.shape[0] or n > positions.shape[0] or heads * head_stride > x.shape[1]:
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("rope").ayk_rope(
+        _ptr(x), c_int(x.stride(0)), _ptr(positions), _ptr(freq), c_int(n), c_int(heads),
+        c_int(head_stride), c_int(offset), c_int(2 * freq.shape[0]), c_int(ROPE_LAYOUTS[layout]),
+        c_int(_TYPE[x.dtype]), _stream())
+    check(status, op)
+
+
+# ---- latent attention -----------------------------------------------------------------------
+
+def latent_prepare(proj: torch.Tensor, *, kv_offset: int, latent_weight: torch.Tensor,
+                   eps: float, positions: torch.Tensor, slot_mapping: torch.Tensor | None,
+                   freq: torch.Tensor, layout: str, pages: torch.Tensor | None,
+                   q_plain: torch.Tensor, qa: torch.Tensor, heads: int, dim: int, rot: int,
+                   rank: int, rows: int) -> None:
+    """From a row of the fused projection (float32: the heads' queries ``[dim | rot]``, then
+    at ``kv_offset`` the raw latent of ``rank`` entries and the raw shared key piece of
+    ``rot``): the latent normalised by its root mean square times ``latent_weight`` and the
+    rotated key piece go to the row's cache slot (``pages`` ``[page, 1, slot, rank + rot]``),
+    the unrotated query parts to ``q_plain`` ``[N, heads * dim]``, the rotated ones to
+    ``qa[:, h, rank:]`` (``qa`` is ``[N, heads * (rank + rot)]``)."""
+    op = "latent_prepare"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "proj", proj, torch.float32, 2)
+    _need(op, "latent_weight", latent_weight, torch.float32, 1)
+    _need(op, "positions", positions, torch.int32, 1)
+    _need(op, "freq", freq, torch.float64, 1)
+    _need(op, "q_plain", q_plain, ndim=2)
+    _need(op, "qa", qa, q_plain.dtype, 2)
+    if q_plain.dtype not in _TYPE or layout not in ROPE_LAYOUTS:
+        raise BackendError(f"{op}: float32 or bfloat16 and a known layout only")
+    if pages is not None:
+        _need(op, "pages", pages, q_plain.dtype, 4)
+        if slot_mapping is None or not pages.is_contiguous() or pages.shape[1] != 1 or \
+                pages.shape[3] != rank + rot:
+            raise BackendError(f"{op}: pages must be contiguous [page, 1, slot, rank + rot] "
+                               "and come with a slot mapping")
+        _need(op, "slot_mapping", slot_mapping, torch.int32, 1)
+    if rows > proj.shape[0] or rows > positions.shape[0] or rows > q_plain.shape[0] or \
+            rows > qa.shape[0] or latent_weight.shape[0] != rank or \
+            q_plain.shape[1] != heads * dim or qa.shape[1] != heads * (rank + rot) or \
+            proj.shape[1] < kv_offset + rank + rot or \
+            (slot_mapping is not None and rows > slot_mapping.shape[0]):
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("latent_attention").ayk_latent_prepare(
+        _ptr(proj), c_int(proj.stride(0)), c_int(kv_offset), _ptr(latent_weight), c_float(eps),
+        _ptr(positions), _ptr(slot_mapping if pages is not None else None), _ptr(freq),
+        c_int(2 * freq.shape[0]), c_int(ROPE_LAYOUTS[layout]), _ptr(pages), _ptr(q_plain),
+        c_int(q_plain.stride(0)), _ptr(qa), c_int(qa.stride(0)), c_int(rows), c_int(heads),
+        c_int(dim), c_int(rot), c_int(rank), c_int(_TYPE[q_plain.dtype]), _stream())
+    check(status, op)
+
+
+def head_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, heads: int,
+                transposed: bool, rows: int, gate: torch.Tensor | None = None) -> None:
+    """One small product per head, fp32 sums in a fixed order.
+
+    ``a`` is ``[N, heads * I]`` and ``out`` ``[N, heads * J']`` with ``J' >= J`` (a head's
+    results start every ``out.shape[1] / heads`` columns). ``weight`` holds the heads' matrices
+    one under the other: ``[heads * J, I]`` applied as ``W_h a_h`` (``transposed=False``), or
+    ``[heads * I, J]`` applied as ``W_h^T a_h`` (``transposed=True``). With ``gate`` (float32
+    ``[N, heads * J]``) the result is multiplied by ``sigmoid(gate)``."""
+    op = "head_linear"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "a", a, ndim=2)
+    _need(op, "weight", weight, a.dtype, 2)
+    _need(op, "out", out, a.dtype, 2)
+    if a.dtype not in _TYPE or not weight.is_contiguous():
+        raise BackendError(f"{op}: float32 or bfloat16 and a contiguous weight only")
+    if heads < 1 or a.shape[1] % heads or out.shape[1] % heads or weight.shape[0] % heads:
+        raise BackendError(f"{op}: {heads} heads do not divide the widths")
+    inner = a.shape[1] // heads
+    if transposed:
+        if weight.shape[0] // heads != inner:
+            raise BackendError(f"{op}: the weight's rows per head are not a's columns per head")
+        outer, w_in, w_out = weight.shape[1], weight.shape[1], 1
+    else:
+        if weight.shape[1] != inner:
+            raise BackendError(f"{op}: the weight's columns are not a's columns per head")
+        outer, w_in, w_out = weight.shape[0] // heads, 1, weight.shape[1]
+    out_head = out.shape[1] // heads
+    if outer > out_head or rows > a.shape[0] or rows > out.shape[0]:
+        raise BackendError(f"{op}: shapes do not fit")
+    if gate is not None:
+        _need(op, "gate", gate, torch.float32, 2)
+        if gate.shape[1] != heads * outer or gate.shape[0] < rows:
+            raise BackendError(f"{op}: the gate does not match the result")
+    status = library("latent_attention").ayk_head_linear(
+        _ptr(a), c_int(a.stride(0)), c_int(inner), _ptr(weight),
+        c_longlong(weight.shape[0] // heads * weight.shape[1]), c_int(w_in), c_int(w_out),
+        _ptr(gate), c_int(0 if gate is None else gate.stride(0)), _ptr(out),
+        c_int(out.stride(0)), c_int(out_head), c_int(rows), c_int(heads), c_int(inner),
+        c_int(outer), c_int(_TYPE[a.dtype]), _stream())
+    check(status, op)
+
+
+def latent_attention(qa: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                     request_of_row: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+                     *, num_heads: int, rank: int, scale: float, window: int = 0,
+                     rows: int | None = None) -> None:
+    """Attention of all heads over one latent row per token: the row of request
+    ``request_of_row[i]`` at ``positions[i]`` scores ``scale * qa[i, h] . page_row`` over keys
+    ``max(0, p - window + 1) .. p`` (``window`` 0: all) and returns the softmax-weighted sum of
+    the page rows' first ``rank`` entries: ``out`` is ``[N, num_heads * rank]``. ``pages`` is
+    ``[page, 1, slot, rank + rot]``; the step's own rows must already be stored."""
+    op = "latent_attention"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "qa", qa, ndim=2)
+    _need(op, "out", out, qa.dtype, 2)
+    _need(op, "pages", pages, qa.dtype, 4)
+    _need(op, "block_table", block_table, torch.int32, 2)
+    _need(op, "request_of_row", request_of_row, torch.int32, 1)
+    _need(op, "positions", positions, torch.int32, 1)
+    if qa.dtype not in _TYPE or not pages.is_contiguous() or pages.shape[1] != 1:
+        raise BackendError(f"{op}: contiguous float32 or bfloat16 pages [page, 1, slot, row]")
+    _, _, page_size, key_dim = pages.shape
+    n = qa.shape[0] if rows is None else rows
+    if qa.shape[1] != num_heads * key_dim or out.shape[1] != num_heads * rank or \
+            rank > key_dim or n > out.shape[0] or n > request_of_row.shape[0] or \
+            n > positions.shape[0]:
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("latent_attention").ayk_latent_attention(
+        _ptr(qa), c_int(qa.stride(0)), _ptr(pages), _ptr(block_table),
+        c_int(block_table.stride(0)), _ptr(request_of_row), _ptr(positions), _ptr(out),
+        c_int(out.stride(0)), c_int(n), c_int(num_heads), c_int(rank), c_int(key_dim - rank),
+        c_int(page_size), c_float(scale), c_int(window), c_int(_TYPE[qa.dtype]), _stream())
+    check(status, op)
+
+
+# ---- layers with a running state ------------------------------------------------------------
+
+#: columns of a matrix state that one CTA of the scan kernels owns (``SCAN_COLS`` in
+#: ``csrc/recurrent.cu``); the mLSTM state keeps its normaliser and maximum once per such tile
+SCAN_COLUMNS = 16
+
+
+def scan_state_floats(kind: str, *, heads: int, inner: int, columns: int, taps: int = 1,
+                      channels: int = 0) -> int:
+    """Floats of one request's state: ``"mamba2"``: the ``taps - 1`` kept inputs of
+    ``channels`` channels, then ``heads`` matrices ``[inner, columns]``; ``"mlstm"``: ``heads``
+    matrices ``[inner, columns]``, then a normaliser ``[inner]`` and a maximum per head and
+    tile of ``SCAN_COLUMNS`` columns."""
+    matrices = heads * inner * columns
+    if kind == "mamba2":
+        return (taps - 1) * channels + matrices
+    if kind == "mlstm":
+        tiles = -(-columns // SCAN_COLUMNS)
+        return matrices + heads * tiles * (inner + 1)
+    raise BackendError(f"scan_state_floats: unknown kind {kind!r}")
+
+
+def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+                     state: torch.Tensor, out: torch.Tensor, *, request_of_row: torch.Tensor,
+                     row_start: torch.Tensor, state_slot: torch.Tensor, rows: int,
+                     requests: int) -> None:
+    """``out = silu(bias + causal convolution of x per channel)`` for the step's rows
+    (float32 ``[N, channels]``; ``weight`` ``[channels, taps]``, its last column the current
+    row's), with the ``taps - 1`` inputs before each request's first row taken from
+    ``state[slot, :(taps - 1) * channels]``, which is then moved on to the step's end."""
+    op = "causal_conv_silu"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "x", x, torch.float32, 2)
+    _need(op, "weight", weight, torch.float32, 2)
+    _need(op, "state", state, torch.float32, 2)
+    _need(op, "out", out, torch.float32, 2)
+    channels, taps = weight.shape
+    if bias is not None:
+        _need(op, "bias", bias, torch.float32, 1)
+    if x.shape[1] != channels or out.shape[1] != channels or rows > x.shape[0] or \
+            rows > out.shape[0] or state.shape[1] < (taps - 1) * channels or \
+            not weight.is_contiguous() or (bias is not None and bias.shape[0] != channels):
+        raise BackendError(f"{op}: shapes do not fit")
+    global _launches
+    _launches += 1 if taps > 1 else 0  # the update of the kept inputs is a launch of its own
+    status = library("recurrent").ayk_causal_conv_silu(
+        _ptr(x), c_int(x.stride(0)), _ptr(weight), _ptr(bias), _ptr(state),
+        c_longlong(state.stride(0)), _ptr(request_of_row), _ptr(row_start), _ptr(state_slot),
+        _ptr(out), c_int(out.stride(0)), c_int(rows), c_int(requests), c_int(channels),
+        c_int(taps), _stream())
+    check(status, op)
+
+
+def mamba2_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor,
+                a_log: torch.Tensor, skip: torch.Tensor | None, state: torch.Tensor,
+                y: torch.Tensor, *, row_start: torch.Tensor, state_slot: torch.Tensor,
+                requests: int, heads: int, groups: int, state_size: int, columns: int) -> None:
+    """The state-space recurrence over each request's rows. ``xbc`` float32
+    ``[N, heads * columns + 2 * groups * state_size]`` (x, then B, then C, after convolution
+    and activation), ``dt_raw`` ``[N, heads]``; per head ``S <- exp(-exp(a_log) dt) S + dt B
+    x^T``, ``y = S^T C + skip * x`` with ``dt = softplus(dt_raw + dt_bias)``. ``state``
+    ``[slots, heads * state_size * columns]`` (a view of the matrices' part of the state)."""
+    op = "mamba2_scan"
+    if _left_out and op in _left_out:
+        return
+    for name, tensor in (("xbc", xbc), ("dt_raw", dt_raw), ("state", state), ("y", y)):
+        _need(op, name, tensor, torch.float32, 2)
+    for name, tensor in (("dt_bias", dt_bias), ("a_log", a_log)):
+        _need(op, name, tensor, torch.float32, 1)
+        if tensor.shape[0] != heads:
+            raise BackendError(f"{op}: {name} must have one entry per head")
+    if xbc.shape[1] != heads * columns + 2 * groups * state_size or dt_raw.shape[1] != heads or \
+            y.shape[1] != heads * columns or state.shape[1] < heads * state_size * columns:
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("recurrent").ayk_mamba2_scan(
+        _ptr(xbc), c_int(xbc.stride(0)), _ptr(dt_raw), c_int(dt_raw.stride(0)), _ptr(dt_bias),
+        _ptr(a_log), _ptr(skip), _ptr(state), c_longlong(state.stride(0)), _ptr(row_start),
+        _ptr(state_slot), _ptr(y), c_int(y.stride(0)), c_int(requests), c_int(heads),
+        c_int(groups), c_int(state_size), c_int(columns), _stream())
+    check(status, op)
+
+
+def mlstm_scan(proj: torch.Tensor, gate_bias: torch.Tensor | None, state: torch.Tensor,
+               out: torch.Tensor, *, row_start: torch.Tensor, state_slot: torch.Tensor,
+               requests: int, heads: int, dim: int, columns: int, k_offset: int, v_offset: int,
+               i_offset: int, f_offset: int, cap: float) -> None:
+    """The matrix-memory recurrence over each request's rows. ``proj`` float32 rows hold the
+    queries at 0, keys at ``k_offset`` (``heads * dim`` each), values at ``v_offset``
+    (``heads * columns``) and the raw input and forget gates at ``i_offset`` / ``f_offset``
+    (``heads`` each); ``gate_bias`` ``[2 * heads]`` (input, then forget). ``out``
+    ``[N, heads * columns]`` is the memory's answer before norm and output gate. ``state``
+    ``[slots, scan_state_floats("mlstm", ...)]``."""
+    op = "mlstm_scan"
+    if _left_out and op in _left_out:
+        return
+    for name, tensor in (("proj", proj), ("state", state), ("out", out)):
+        _need(op, name, tensor, torch.float32, 2)
+    if gate_bias is not None:
+        _need(op, "gate_bias", gate_bias, torch.float32, 1)
+    need = scan_state_floats("mlstm", heads=heads, inner=dim, columns=columns)
+    if state.shape[1] < need or out.shape[1] != heads * columns or \
+            proj.shape[1] < max(k_offset + heads * dim, v_offset + heads * columns,
+                                i_offset + heads, f_offset + heads) or \
+            (gate_bias is not None and gate_bias.shape[0] != 2 * heads):
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("recurrent").ayk_mlstm_scan(
+        _ptr(proj), c_int(proj.stride(0)), c_int(k_offset), c_int(v_offset), c_int(i_offset),
+        c_int(f_offset), _ptr(gate_bias), c_float(cap), _ptr(state),
+        c_longlong(state.stride(0)), _ptr(row_start), _ptr(state_slot), _ptr(out),
+        c_int(out.stride(0)), c_int(requests), c_int(heads), c_int(dim), c_int(columns),
+        _stream())
     check(status, op)

@@ -59,13 +59,19 @@ def resolve_architecture(name: object) -> Architecture:
 
 
 def architecture_of(config_json: Mapping[str, object]) -> Architecture:
-    """The architecture a parsed ``config.json`` names in ``architectures[0]``."""
+    """The architecture a parsed ``config.json`` names: ``architectures[0]``, or the string
+    under ``architecture`` in files that name exactly one."""
     names = config_json.get("architectures")
-    if not isinstance(names, (list, tuple)) or not names:
-        raise ModelLoadError("config.json has no 'architectures' list; cannot choose a model",
-                             context={"missing": ("architecture",)})
-    return resolve_architecture(names[0])
+    if isinstance(names, (list, tuple)) and names:
+        return resolve_architecture(names[0])
+    name = config_json.get("architecture")
+    if isinstance(name, str) and name:
+        return resolve_architecture(name)
+    raise ModelLoadError("config.json has neither an 'architectures' list nor an "
+                         "'architecture' name; cannot choose a model",
+                         context={"missing": ("architecture",)})
 
 
 def _builtin() -> None:
     import ayaka_b200.models.gpt2  # noqa: F401  (registers itself)
+    import ayaka_b200.models.mapuvik  # noqa: F401

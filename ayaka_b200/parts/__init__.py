@@ -5,7 +5,8 @@ Importing this package registers the built-in kinds: mixer ``attention``; feed-f
 embedding ``token``; head ``linear``.
 """
 
-from ayaka_b200.parts import block, embedding, feed_forward, mixer, norm  # noqa: F401
+from ayaka_b200.parts import (block, embedding, feed_forward, latent, mixer, norm,  # noqa: F401
+                              recurrent)
 from ayaka_b200.parts.base import (BuildContext, CacheNeed, Part, StateNeed, build_part,
                                    register_part, registered_kinds)
 from ayaka_b200.parts.context import GroupStep, LayerCache, StepContext, Workspace

@@ -42,6 +42,7 @@ class CacheNeed:
     num_kv_heads: int
     head_dim: int
     window: int = 0  # 0: every earlier key; n > 0: the last n keys
+    values: bool = True  # False: one row per token only (a latent cache): no value pages
 
 
 @dataclass(frozen=True, slots=True)

@@ -8,7 +8,7 @@ from ayaka_b200.parts.base import BuildContext, Part, build_part, register_part
 from ayaka_b200.parts.context import LayerCache, StepContext, Workspace
 from ayaka_b200.parts.spec import LayerSpec
 
-__all__ = ["Block", "PreNormBlock"]
+__all__ = ["Block", "ParallelBlock", "PreNormBlock"]
 
 
 class Block(Part):
@@ -68,6 +68,32 @@ class PreNormBlock(Block):
         else:
             self.feed_forward_norm.forward(residual, hidden, count=n)  # type: ignore
             self.feed_forward.forward(hidden, residual, step)  # type: ignore[attr-defined]
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Block):
+    """``h = norm(x); x += mixer(h) + feed_forward(h)``: one norm, and both halves read its
+    output. Each half adds its result into the fp32 residual stream in the epilogue of its
+    last matrix product, the mixer first. The layer's norm is ``spec.mixer_norm``
+    (``spec.feed_forward_norm`` is not built)."""
+
+    def __init__(self, spec: LayerSpec, ctx: BuildContext, position: Part | None) -> None:
+        super().__init__(ctx)
+        self.mixer_norm = self.add_child(
+            "mixer_norm", build_part("norm", spec.mixer_norm.kind, spec.mixer_norm, ctx))
+        self.mixer = self.add_child(
+            "mixer", build_part("mixer", spec.mixer.kind, spec.mixer, ctx, position))
+        self.feed_forward = self.add_child(
+            "feed_forward",
+            build_part("feed_forward", spec.feed_forward.kind, spec.feed_forward, ctx))
+        self.width = int(spec.mixer_norm.width)  # type: ignore[arg-type]
+
+    def forward(self, residual: torch.Tensor, step: StepContext, cache: LayerCache) -> None:
+        # a buffer of its own: the halves' own scratch must not overwrite what both read
+        hidden = step.workspace.buffer("block.shared_normed", self.width, self.ctx.dtype)
+        self.mixer_norm.forward(residual, hidden, count=step.num_rows)  # type: ignore
+        self.mixer.forward(hidden, residual, step, cache)  # type: ignore[attr-defined]
+        self.feed_forward.forward(hidden, residual, step)  # type: ignore[attr-defined]
 
 
 def _plain_norm(norm: Part) -> bool:

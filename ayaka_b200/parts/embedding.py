@@ -9,7 +9,8 @@ from ayaka_b200.parts.base import BuildContext, Part, register_part
 from ayaka_b200.parts.context import StepContext
 from ayaka_b200.parts.spec import PartSpec
 
-__all__ = ["LearnedPositions", "LinearHead", "NoPositions", "PositionEncoding", "TokenEmbedding"]
+__all__ = ["LearnedPositions", "LinearHead", "NoPositions", "PositionEncoding",
+           "RotaryPositions", "TokenEmbedding"]
 
 
 class PositionEncoding(Part):
@@ -55,6 +56,40 @@ class NoPositions(PositionEncoding):
 
     def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
         super().__init__(ctx)
+
+
+@register_part("position", "rotary")
+class RotaryPositions(PositionEncoding):
+    """Rotation of queries and keys by their positions, before the keys are cached: in every
+    head the first ``dims`` entries are turned, pair ``i`` by ``position * base^(-2i/dims)``;
+    the pair is entries ``(2i, 2i+1)`` (``layout="neighbours"``) or ``(i, i + dims/2)``
+    (``"halves"``). No parameter.
+
+    Spec parameters: ``dims``, ``base``, ``head_dim``, ``layout`` (``neighbours`` when absent),
+    ``max_positions`` (optional).
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
+        super().__init__(ctx)
+        self.dims = int(spec.dims)  # type: ignore[arg-type]
+        self.base = float(spec.base)  # type: ignore[arg-type]
+        self.head_dim = int(spec.head_dim)  # type: ignore[arg-type]
+        self.layout = str(spec.get("layout", "neighbours"))
+        limit = spec.get("max_positions")
+        self.max_positions = None if limit is None else int(limit)  # type: ignore[arg-type]
+        if self.dims % 2 or not 0 < self.dims <= self.head_dim:
+            raise ValueError(f"rotary dims must be even and at most head_dim, got {self.dims}")
+        self._freq: torch.Tensor | None = None
+
+    def frequencies(self) -> torch.Tensor:
+        if self._freq is None:
+            self._freq = ops.rope_frequencies(self.dims, self.base, self.ctx.device)
+        return self._freq
+
+    def on_query_key(self, q: torch.Tensor, k: torch.Tensor, step: StepContext) -> None:
+        for rows in (q, k):
+            ops.rope(rows, step.positions, self.frequencies(), heads=rows.shape[1] // self.head_dim,
+                     head_stride=self.head_dim, layout=self.layout, rows=step.num_rows)
 
 
 @register_part("embedding", "token")

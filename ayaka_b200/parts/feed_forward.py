@@ -9,7 +9,7 @@ from ayaka_b200.parts.base import BuildContext, Part, register_part
 from ayaka_b200.parts.context import StepContext, Workspace
 from ayaka_b200.parts.spec import PartSpec
 
-__all__ = ["DenseMLP", "FeedForward"]
+__all__ = ["DenseMLP", "FeedForward", "NoFeedForward"]
 
 
 class FeedForward(Part):
@@ -19,6 +19,17 @@ class FeedForward(Part):
 
     def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext) -> None:
         raise NotImplementedError
+
+
+@register_part("feed_forward", "none")
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: no parameter, no launch."""
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
+        super().__init__(ctx)
+
+    def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext) -> None:
+        return None
 
 
 @register_part("feed_forward", "dense")

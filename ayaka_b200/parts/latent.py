@@ -1,0 +1,100 @@
+"""Latent attention: keys and values are up-projections of one small cached row per token."""
+
+from __future__ import annotations
+
+import torch
+
+from ayaka_b200.kernels import ops
+from ayaka_b200.parts.base import BuildContext, CacheNeed, Part, register_part
+from ayaka_b200.parts.context import LayerCache, StepContext
+from ayaka_b200.parts.mixer import Mixer
+from ayaka_b200.parts.spec import PartSpec
+
+__all__ = ["LatentAttention"]
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    """Multi-head attention over a low-rank cache.
+
+    One fused projection of the normed input gives, per row, the heads' queries
+    (``[dim unrotated | rot rotated]`` each), a raw latent of ``rank`` entries with one raw
+    key piece of ``rot`` entries that all heads share, and the output gate. The latent is
+    normalised by its root mean square (plain weight), the key piece and the queries' rotated
+    parts are turned by the position (``rot_dims`` of their ``rot`` entries), and only
+    ``[latent | key piece]`` goes to the cache: ``rank + rot`` values per token whatever the
+    number of heads. Head ``h`` scores ``scale * (q_plain . W_uk,h c + q_rot . kr)`` over the
+    last ``window`` keys (0: all) and sums ``W_uv,h c`` with softmax weights; the joined heads
+    are multiplied by ``sigmoid(gate)`` and projected back into the residual stream.
+
+    The up-projections are applied on the query's side (``W_uk,h^T q_plain`` before the
+    scores, ``W_uv,h`` after the weighted sum of latents), never to cached rows:
+    ``csrc/latent_attention.cu``.
+
+    Spec parameters: ``width``, ``num_heads``, ``dim``, ``rot``, ``value_dim``, ``rank``,
+    ``scale``, ``window`` (0 = none), ``rot_dims``, ``rot_base``, ``rot_layout``
+    (``neighbours`` when absent), ``eps`` (of the latent's norm).
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext, position: Part | None = None) -> None:
+        super().__init__(ctx)
+        self.width = int(spec.width)  # type: ignore[arg-type]
+        self.num_heads = int(spec.num_heads)  # type: ignore[arg-type]
+        self.dim = int(spec.dim)  # type: ignore[arg-type]
+        self.rot = int(spec.rot)  # type: ignore[arg-type]
+        self.value_dim = int(spec.value_dim)  # type: ignore[arg-type]
+        self.rank = int(spec.rank)  # type: ignore[arg-type]
+        self.scale = float(spec.scale)  # type: ignore[arg-type]
+        self.window = int(spec.get("window", 0))  # type: ignore[arg-type]
+        self.rot_dims = int(spec.get("rot_dims", self.rot))  # type: ignore[arg-type]
+        self.rot_base = float(spec.rot_base)  # type: ignore[arg-type]
+        self.rot_layout = str(spec.get("rot_layout", "neighbours"))
+        self.eps = float(spec.eps)  # type: ignore[arg-type]
+        if self.rot_dims % 2 or not 0 <= self.rot_dims <= self.rot:
+            raise ValueError(f"rot_dims must be even and at most rot ({self.rot}), got "
+                             f"{self.rot_dims}")
+        if min(self.num_heads, self.rank, self.value_dim) < 1 or self.dim < 1 or self.window < 0:
+            raise ValueError("latent attention needs heads, dim, rank and value_dim >= 1")
+        self.q_width = self.num_heads * (self.dim + self.rot)
+        self.kv_width = self.rank + self.rot
+        self.out_width = self.num_heads * self.value_dim
+        # queries, then the raw latent and key piece, then the gate: one product
+        self.proj_weight = self.add_param(
+            "proj.weight", (self.q_width + self.kv_width + self.out_width, self.width), "matrix")
+        self.latent_norm = self.add_param("latent_norm.weight", (self.rank,), "vector")
+        self.up_key = self.add_param("up_key.weight", (self.num_heads * self.dim, self.rank),
+                                     "matrix")
+        self.up_value = self.add_param("up_value.weight", (self.out_width, self.rank), "matrix")
+        self.out_weight = self.add_param("out.weight", (self.width, self.out_width), "matrix")
+        self._freq: torch.Tensor | None = None
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(1, self.kv_width, self.window, values=False)
+
+    def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext,
+                cache: LayerCache) -> None:
+        n, dtype, work = step.num_rows, self.ctx.dtype, step.workspace
+        heads, rank = self.num_heads, self.rank
+        if self._freq is None:
+            self._freq = ops.rope_frequencies(max(self.rot_dims, 0), self.rot_base, hidden.device)
+        group = step.groups[cache.group]  # type: ignore[index]
+        proj = work.buffer("latent.proj", self.proj_weight.shape[0], torch.float32)
+        q_plain = work.buffer("latent.q_plain", heads * self.dim, dtype)
+        qa = work.buffer("latent.query", heads * self.kv_width, dtype)
+        mixed = work.buffer("latent.mixed", heads * rank, dtype)
+        attended = work.buffer("latent.out", self.out_width, dtype)
+        ops.linear(hidden, self.proj_weight, None, proj, rows=n)
+        ops.latent_prepare(
+            proj, kv_offset=self.q_width, latent_weight=self.latent_norm, eps=self.eps,
+            positions=step.positions, slot_mapping=group.slot_mapping, freq=self._freq,
+            layout=self.rot_layout, pages=cache.k_pages if cache.writes else None,
+            q_plain=q_plain, qa=qa, heads=heads, dim=self.dim, rot=self.rot, rank=rank, rows=n)
+        # the queries' unrotated parts, taken to latent space: qa[:, h, :rank] = W_uk,h^T q
+        ops.head_linear(q_plain, self.up_key, qa, heads=heads, transposed=True, rows=n)
+        ops.latent_attention(qa, cache.k_pages, group.block_table, step.request_of_row,
+                             step.positions, mixed, num_heads=heads, rank=rank,
+                             scale=self.scale, window=self.window, rows=n)
+        gate = proj[:, self.q_width + self.kv_width:]
+        ops.head_linear(mixed, self.up_value, attended, heads=heads, transposed=False, rows=n,
+                        gate=gate)
+        ops.linear(attended, self.out_weight, None, residual, residual=True, rows=n)

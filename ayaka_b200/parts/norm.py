@@ -8,7 +8,7 @@ from ayaka_b200.kernels import ops
 from ayaka_b200.parts.base import BuildContext, Part, register_part
 from ayaka_b200.parts.spec import PartSpec
 
-__all__ = ["LayerNorm"]
+__all__ = ["LayerNorm", "RMSNorm"]
 
 
 @register_part("norm", "layer_norm")
@@ -39,3 +39,26 @@ class LayerNorm(Part):
                 rows: torch.Tensor | None = None) -> None:
         """Normalise ``count`` fp32 rows of ``x`` (gathered by ``rows`` if given) into ``out``."""
         ops.layer_norm(x, self.weight, self.bias, self.eps, out, rows=rows, count=count)
+
+
+@register_part("norm", "rms_norm")
+class RMSNorm(Part):
+    """``x / sqrt(mean(x^2) + eps) * (offset + weight)`` over the last dimension, in fp32 from
+    the fp32 residual stream, rounded once to the output's dtype. ``offset`` is 0 for a plain
+    weight and 1 for a weight that is stored as its deviation from one.
+
+    Spec parameters: ``width``, ``eps``, ``offset`` (0 when absent).
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
+        super().__init__(ctx)
+        self.width = int(spec.width)  # type: ignore[arg-type]
+        self.eps = float(spec.eps)  # type: ignore[arg-type]
+        self.offset = float(spec.get("offset", 0.0))  # type: ignore[arg-type]
+        self.weight = self.add_param("weight", (self.width,), "vector")
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, *, count: int,
+                rows: torch.Tensor | None = None) -> None:
+        """Normalise ``count`` fp32 rows of ``x`` (gathered by ``rows`` if given) into ``out``."""
+        ops.rms_norm(x, self.weight, self.eps, out, weight_offset=self.offset, rows=rows,
+                     count=count)
