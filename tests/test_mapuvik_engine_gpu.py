@@ -1,0 +1,121 @@
+"""Mapuvik through the engine against the plain implementation: whole prompts, prompts then
+token-by-token decoding, portions of every size, mixed batches with pages and state slots
+used again, long decoding past every window, the first tokens, greedy generation through
+``LLM`` and its scheduler, and the replay program as a child process."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import engine_support as support
+import plain_mapuvik as plain
+from cases import random_tokens
+from mapuvik_cases import (LOUD, LOUD_WIDE, TINY_A, TINY_B, TINY_C, TINY_STATE_ONLY,
+                           plain_logits)
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = {"a": (TINY_A, LOUD), "b": (TINY_B, LOUD), "c": (TINY_C, LOUD_WIDE),
+           "state_only": (TINY_STATE_ONLY, LOUD)}
+#: lengths around the windows (7, 20, 48) and the page (16) of the configurations
+LENGTHS = (1, 2, 37, 95, 16, 150)
+
+
+def _sequences(config: dict, lengths=LENGTHS, seed: int = 0) -> dict[str, list[int]]:
+    return {f"r{index}": random_tokens(config["vocab"], length, 50 * seed + index)
+            for index, length in enumerate(lengths)}
+
+
+def _model(tmp_path, name: str, dtype: str):
+    config, init = CONFIGS[name]
+    folder, state = support.make_model(tmp_path / f"{name}-{dtype}", config, 7, init, dtype)
+    return config, folder, state
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "state_only"])
+def test_the_four_ways_of_cutting_the_work_agree_with_the_plain_model(tmp_path, name, dtype):
+    config, folder, state = _model(tmp_path, name, dtype)
+    sequences = _sequences(config)
+    expected = plain_logits(state, config, sequences)
+    for label, steps, blocks in (
+            ("whole", support.schedule_whole(sequences), 24),
+            ("tail", support.schedule_tail(sequences, tail=40), 24),
+            ("portions", support.schedule_portions(sequences), 24),
+            # 320 tokens of cache for six requests of 301 tokens: pages and slots come back
+            ("mixed", support.schedule_mixed(sequences, pool_tokens=320), 21)):
+        core = support.build_core(folder, dtype, num_blocks=blocks, max_running=4)
+        got = support.replay(core, steps)
+        support.assert_logits_close(got, expected, dtype, f"mapuvik-{name}/{label}")
+        assert not core.manager.live_requests()
+        del core
+
+
+@pytest.mark.parametrize("page", [8, 32])
+def test_other_page_sizes(tmp_path, page):
+    config, folder, state = _model(tmp_path, "b", "float32")
+    sequences = _sequences(config, (3, 70, 33), seed=2)
+    expected = plain_logits(state, config, sequences)
+    core = support.build_core(folder, "float32", num_blocks=1 + 192 // page, block_size=page,
+                              max_tokens_per_step=64)
+    got = support.replay(core, support.schedule_mixed(sequences, pool_tokens=192))
+    support.assert_logits_close(got, expected, "float32", f"mapuvik-b/page{page}", page=page)
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_long_decoding_from_the_first_token(tmp_path, name):
+    """One prompt token, then 230 single tokens: every window passes over decoded tokens,
+    pages behind a window are given back and handed out again, states run long."""
+    config, folder, state = _model(tmp_path, name, "float32")
+    sequences = _sequences(config, (231,), seed=3)
+    expected = plain_logits(state, config, sequences)
+    core = support.build_core(folder, "float32", num_blocks=17, max_running=1)
+    got = support.replay(core, support.schedule_tail(sequences, tail=230))
+    support.assert_logits_close(got, expected, "float32", f"mapuvik-{name}/long-decode")
+
+
+def test_a_batch_gives_each_request_what_it_gets_alone(tmp_path):
+    """The same requests alone and side by side (portions beside single tokens): equal to a
+    few rounding steps of float32, whatever row, slot or page a request got."""
+    config, folder, _ = _model(tmp_path, "a", "float32")
+    sequences = _sequences(config, (60, 5, 33, 18), seed=4)
+    alone = support.replay(support.build_core(folder, "float32", num_blocks=24),
+                           support.schedule_portions(sequences, sizes=(7, 2, 30, 1)))
+    core = support.build_core(folder, "float32", num_blocks=12)
+    together = support.replay(core, support.schedule_mixed(sequences, pool_tokens=160))
+    for rid in sequences:
+        scale = float(alone[rid].abs().max())
+        assert float((alone[rid] - together[rid]).abs().max()) <= 2e-5 * scale, rid
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_through_the_entry_point(tmp_path, graphs):
+    from ayaka_b200 import LLM, EngineConfig, SamplingParams
+
+    config, folder, state = _model(tmp_path, "a", "float32")
+    prompts = [random_tokens(config["vocab"], n, 90 + n) for n in (1, 9, 40, 17, 3, 26)]
+    wide = plain.cast_state(state, torch.float64)
+    # a small budget and pool: prompts are cut into portions beside decoding requests, more
+    # requests than running slots, so state slots and pages are used again
+    engine = EngineConfig(model=str(folder), dtype="float32", max_running=3, num_blocks=20,
+                          max_tokens_per_step=24, cuda_graph=graphs)
+    with LLM.from_config(engine) as llm:
+        outputs = llm.generate([tuple(p) for p in prompts],
+                               SamplingParams(temperature=0.0, max_tokens=12))
+        llm.core.manager.check_integrity()
+        assert not llm.core.manager.live_requests()
+    for prompt, output in zip(prompts, outputs):
+        assert output.error is None
+        assert list(output.outputs[0].token_ids) == plain.greedy_generate(wide, config, prompt, 12)
+
+
+def test_the_replay_program_runs_a_mapuvik_folder(tmp_path):
+    config, folder, state = _model(tmp_path, "b", "float32")
+    sequences = _sequences(config, (41, 2, 19), seed=5)
+    steps = support.schedule_mixed(sequences, pool_tokens=128)
+    got = support.run_trace_program(folder, "float32", steps,
+                                    support.peak_tokens(steps, sequences), tmp_path / "out",
+                                    config["vocab"])
+    support.assert_logits_close(got, plain_logits(state, config, sequences), "float32",
+                                "mapuvik-b/trace_run")
