@@ -821,10 +821,12 @@ def latent_prepare(proj: torch.Tensor, *, kv_offset: int, latent_weight: torch.T
 
 
 def head_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, heads: int,
-                transposed: bool, rows: int, gate: torch.Tensor | None = None) -> None:
+                transposed: bool, rows: int, gate: torch.Tensor | None = None,
+                inner: int | None = None) -> None:
     """One small product per head, fp32 sums in a fixed order.
 
-    ``a`` is ``[N, heads * I]`` and ``out`` ``[N, heads * J']`` with ``J' >= J`` (a head's
+    ``a`` is ``[N, heads * I']`` of which a head's first ``I = inner`` columns are used
+    (all ``I'`` when absent), and ``out`` ``[N, heads * J']`` with ``J' >= J`` (a head's
     results start every ``out.shape[1] / heads`` columns). ``weight`` holds the heads' matrices
     one under the other: ``[heads * J, I]`` applied as ``W_h a_h`` (``transposed=False``), or
     ``[heads * I, J]`` applied as ``W_h^T a_h`` (``transposed=True``). With ``gate`` (float32
@@ -839,7 +841,10 @@ def head_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, hea
         raise BackendError(f"{op}: float32 or bfloat16 and a contiguous weight only")
     if heads < 1 or a.shape[1] % heads or out.shape[1] % heads or weight.shape[0] % heads:
         raise BackendError(f"{op}: {heads} heads do not divide the widths")
-    inner = a.shape[1] // heads
+    a_head = a.shape[1] // heads
+    inner = a_head if inner is None else inner
+    if not 1 <= inner <= a_head:
+        raise BackendError(f"{op}: a head of a has {a_head} columns, not {inner}")
     if transposed:
         if weight.shape[0] // heads != inner:
             raise BackendError(f"{op}: the weight's rows per head are not a's columns per head")
@@ -856,7 +861,7 @@ def head_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, hea
         if gate.shape[1] != heads * outer or gate.shape[0] < rows:
             raise BackendError(f"{op}: the gate does not match the result")
     status = library("latent_attention").ayk_head_linear(
-        _ptr(a), c_int(a.stride(0)), c_int(inner), _ptr(weight),
+        _ptr(a), c_int(a.stride(0)), c_int(a_head), _ptr(weight),
         c_longlong(weight.shape[0] // heads * weight.shape[1]), c_int(w_in), c_int(w_out),
         _ptr(gate), c_int(0 if gate is None else gate.stride(0)), _ptr(out),
         c_int(out.stride(0)), c_int(out_head), c_int(rows), c_int(heads), c_int(inner),

@@ -7,7 +7,7 @@ import torch
 from ayaka_b200.kernels import ops
 from ayaka_b200.parts.base import BuildContext, CacheNeed, Part, register_part
 from ayaka_b200.parts.context import LayerCache, StepContext
-from ayaka_b200.parts.mixer import Mixer
+from ayaka_b200.parts.mixer import Mixer, attend_paged
 from ayaka_b200.parts.spec import PartSpec
 
 __all__ = ["LatentAttention"]
@@ -29,7 +29,12 @@ class LatentAttention(Mixer):
 
     The up-projections are applied on the query's side (``W_uk,h^T q_plain`` before the
     scores, ``W_uv,h`` after the weighted sum of latents), never to cached rows:
-    ``csrc/latent_attention.cu``.
+    ``csrc/latent_attention.cu``. What is left between the two is attention of ``num_heads``
+    query heads over *one* key head whose rows are also its values (the sum over whole rows
+    ``[c | kr]`` holds the sum over ``c`` in its first ``rank`` entries): when ``rank + rot``
+    is a head size the engine's attention kernels take (a multiple of 16 up to 256), those run
+    it, tensor cores and all, with the latent pages as keys and as values; any other size
+    goes to the kernel of ``csrc/latent_attention.cu``.
 
     Spec parameters: ``width``, ``num_heads``, ``dim``, ``rot``, ``value_dim``, ``rank``,
     ``scale``, ``window`` (0 = none), ``rot_dims``, ``rot_base``, ``rot_layout``
@@ -81,7 +86,8 @@ class LatentAttention(Mixer):
         proj = work.buffer("latent.proj", self.proj_weight.shape[0], torch.float32)
         q_plain = work.buffer("latent.q_plain", heads * self.dim, dtype)
         qa = work.buffer("latent.query", heads * self.kv_width, dtype)
-        mixed = work.buffer("latent.mixed", heads * rank, dtype)
+        shared = self.kv_width % 16 == 0 and self.kv_width <= 256
+        mixed = work.buffer("latent.mixed", heads * (self.kv_width if shared else rank), dtype)
         attended = work.buffer("latent.out", self.out_width, dtype)
         ops.linear(hidden, self.proj_weight, None, proj, rows=n)
         ops.latent_prepare(
@@ -91,10 +97,14 @@ class LatentAttention(Mixer):
             q_plain=q_plain, qa=qa, heads=heads, dim=self.dim, rot=self.rot, rank=rank, rows=n)
         # the queries' unrotated parts, taken to latent space: qa[:, h, :rank] = W_uk,h^T q
         ops.head_linear(q_plain, self.up_key, qa, heads=heads, transposed=True, rows=n)
-        ops.latent_attention(qa, cache.k_pages, group.block_table, step.request_of_row,
-                             step.positions, mixed, num_heads=heads, rank=rank,
-                             scale=self.scale, window=self.window, rows=n)
+        if shared:
+            attend_paged(qa, cache.k_pages, cache.k_pages, mixed, step, group, num_heads=heads,
+                         scale=self.scale, window=self.window, dtype=dtype)
+        else:
+            ops.latent_attention(qa, cache.k_pages, group.block_table, step.request_of_row,
+                                 step.positions, mixed, num_heads=heads, rank=rank,
+                                 scale=self.scale, window=self.window, rows=n)
         gate = proj[:, self.q_width + self.kv_width:]
         ops.head_linear(mixed, self.up_value, attended, heads=heads, transposed=False, rows=n,
-                        gate=gate)
+                        gate=gate, inner=rank)
         ops.linear(attended, self.out_weight, None, residual, residual=True, rows=n)

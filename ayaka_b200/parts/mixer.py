@@ -6,11 +6,11 @@ import torch
 
 from ayaka_b200.kernels import ops
 from ayaka_b200.parts.base import BuildContext, CacheNeed, Part, StateNeed, register_part
-from ayaka_b200.parts.context import LayerCache, StepContext, Workspace
+from ayaka_b200.parts.context import GroupStep, LayerCache, StepContext, Workspace
 from ayaka_b200.parts.embedding import PositionEncoding
 from ayaka_b200.parts.spec import PartSpec
 
-__all__ = ["Attention", "Mixer", "leading_single_rows"]
+__all__ = ["Attention", "Mixer", "attend_paged", "leading_single_rows"]
 
 
 #: From this many leading single-row requests on, a step that also holds prompt portions
@@ -27,6 +27,50 @@ def leading_single_rows(host_rows: list[int]) -> int:
             break
         lead += 1
     return lead if LEADING_SINGLE_ROWS <= lead < len(host_rows) else 0
+
+
+def attend_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                 attended: torch.Tensor, step: StepContext, group: GroupStep, *, num_heads: int,
+                 scale: float, window: int, dtype: torch.dtype,
+                 k_new: torch.Tensor | None = None, v_new: torch.Tensor | None = None,
+                 store: bool = False) -> None:
+    """Causal attention of the step's rows over paged keys and values, with the kernel that
+    serves the step: a decode kernel when every request brings one row (``k_new``/``v_new``:
+    the rows' own keys and values when they are not in the pages yet, stored by the kernel
+    with ``store``), in bfloat16 the tensor-core kernels for prompt portions (with the
+    requests that lead the step with a single row each sent to the decode kernel), in
+    float32 the CUDA-core kernel. Except in the first case the step's keys and values must be
+    in the pages already."""
+    n = step.num_rows
+    if step.decode_only:
+        # which decode kernel, and how a pair's keys are shared out, is the library's choice;
+        # `splits` is what the split-KV one takes (at most 8: a cluster merges on chip)
+        reach = min(step.max_kv_len, window) if window else step.max_kv_len
+        splits = ops.decode_splits(n, num_heads, reach, q.device)
+        ops.attention_decode(q, k_pages, v_pages, group.block_table, step.request_of_row,
+                             step.positions, attended, num_heads=num_heads, scale=scale,
+                             window=window, rows=n, splits=splits, k_new=k_new, v_new=v_new,
+                             store=store)
+    elif dtype == torch.bfloat16:
+        # Prompt portions: tensor-core flash attention. The requests that lead the step
+        # with a single row each (the scheduler puts decoding requests first) go to the
+        # decode kernel instead: as tiles of a prompt kernel each would occupy a CTA
+        # built for 64 or 256 rows. Their keys and values are in the cache by now.
+        lead = leading_single_rows(step.host_rows)
+        if lead:
+            reach = min(step.max_kv_len, window) if window else step.max_kv_len
+            ops.attention_decode(q, k_pages, v_pages, group.block_table, step.request_of_row,
+                                 step.positions, attended, num_heads=num_heads, scale=scale,
+                                 window=window, rows=lead,
+                                 splits=ops.decode_splits(lead, num_heads, reach, q.device))
+        ops.attention_prefill(q, k_pages, v_pages, group.block_table[lead:],
+                              step.row_start[lead:], step.kv_len[lead:], attended,
+                              num_heads=num_heads, scale=scale, host_rows=step.host_rows[lead:],
+                              window=window)
+    else:
+        ops.attention(q, k_pages, v_pages, group.block_table, step.request_of_row,
+                      step.positions, attended, num_heads=num_heads, scale=scale, window=window,
+                      rows=n)
 
 
 class Mixer(Part):
@@ -176,38 +220,9 @@ class Attention(Mixer):
         if cache.writes and not step.decode_only and not stored:
             ops.kv_store(k, v, group.slot_mapping, cache.k_pages, cache.v_pages, rows=n)
         attended = step.workspace.buffer("attention.out", self.q_width, self.ctx.dtype)
-        if step.decode_only:
-            # one row per request: a decode kernel (which one, and how a pair's keys are
-            # shared out, is the library's choice; `splits` is what the split-KV one takes)
-            reach = min(step.max_kv_len, self.window) if self.window else step.max_kv_len
-            # (at most 8: a cluster merges the shares on chip, no scratch)
-            splits = ops.decode_splits(n, self.num_heads, reach, q.device)
-            ops.attention_decode(q, cache.k_pages, cache.v_pages, group.block_table,
-                                 step.request_of_row, step.positions, attended,
-                                 num_heads=self.num_heads, scale=self.scale, window=self.window,
-                                 rows=n, splits=splits,
-                                 k_new=k if cache.writes else None,
-                                 v_new=v if cache.writes else None, store=cache.writes)
-        elif self.ctx.dtype == torch.bfloat16:
-            # Prompt portions: tensor-core flash attention. The requests that lead the step
-            # with a single row each (the scheduler puts decoding requests first) go to the
-            # decode kernel instead: as tiles of a prompt kernel each would occupy a CTA
-            # built for 64 or 256 rows. Their keys and values are in the cache by now.
-            lead = leading_single_rows(step.host_rows)
-            if lead:
-                reach = min(step.max_kv_len, self.window) if self.window else step.max_kv_len
-                ops.attention_decode(q, cache.k_pages, cache.v_pages, group.block_table,
-                                     step.request_of_row, step.positions, attended,
-                                     num_heads=self.num_heads, scale=self.scale,
-                                     window=self.window, rows=lead,
-                                     splits=ops.decode_splits(lead, self.num_heads, reach,
-                                                              q.device))
-            ops.attention_prefill(q, cache.k_pages, cache.v_pages, group.block_table[lead:],
-                                  step.row_start[lead:], step.kv_len[lead:], attended,
-                                  num_heads=self.num_heads, scale=self.scale,
-                                  host_rows=step.host_rows[lead:], window=self.window)
-        else:
-            ops.attention(q, cache.k_pages, cache.v_pages, group.block_table,
-                          step.request_of_row, step.positions, attended,
-                          num_heads=self.num_heads, scale=self.scale, window=self.window, rows=n)
+        attend_paged(q, cache.k_pages, cache.v_pages, attended, step, group,
+                     num_heads=self.num_heads, scale=self.scale, window=self.window,
+                     dtype=self.ctx.dtype, k_new=k if cache.writes else None,
+                     v_new=v if cache.writes else None,
+                     store=cache.writes and step.decode_only)
         ops.linear(attended, self.out_weight, self.out_bias, residual, residual=True, rows=n)

@@ -19,7 +19,8 @@ time and by the measured copy bandwidth. ``points`` holds decode at batch 1 and 
 class costs inside the step (the step replayed as a CUDA graph with and without the class)
 and its fraction of the roofline that bounds it. ``workloads`` holds the two serving
 workloads of BASELINE.json's other configurations (see :func:`workload_run`);
-``--workload small|large`` runs one of them alone and prints a line of its own.
+``--workload small|large`` runs one of them alone and prints a line of its own;
+``--design mapuvik`` runs that design beside GPT-2 of equal size (``bench_design.py``).
 """
 
 from __future__ import annotations
@@ -516,6 +517,11 @@ def main() -> int:
                         help="instead of the headline run: one of the two serving workloads "
                              "(GPT-2 small with 64 ragged requests; GPT-2 large with prompt "
                              "portions beside 32 decoding requests)")
+    parser.add_argument("--design", choices=("mapuvik",),
+                        help="instead of the headline run: the named design beside GPT-2 of "
+                             "equal size, prompt step and decode step with per-kernel times "
+                             "(bench_design.py); --sizes picks among 1024,2048")
+    parser.add_argument("--sizes", default=None, help="with --design: widths to run")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -529,6 +535,11 @@ def main() -> int:
         return 1
     if args.workload:
         print(json.dumps(workload_run(args.workload)))
+        return 0
+    if args.design:
+        import bench_design
+
+        print(json.dumps(bench_design.run(args.sizes)))
         return 0
     warmup = max(args.warmup, 3)
     steps = max(1, min(args.steps, XL["n_positions"] - PROMPT - 2 - warmup))

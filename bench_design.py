@@ -1,0 +1,250 @@
+"""``bench.py --design mapuvik``: prefill and decode throughput of Mapuvik at sizes that
+resemble a real model's layers, beside GPT-2 of the same width, heads, feed-forward and
+number of layers, on one B200 with random bf16 weights.
+
+For each size and model: one prompt step of 2,048 tokens (two prompts of 1,024) and one decode
+step of 8 requests at context 1,025, each timed on the device as a CUDA-graph replay of the
+model's forward (no host time between kernels), and per kernel class: in the prompt step the
+class's own kernels between CUDA events (``ops.timed``), in the decode step the step with and
+without the class (``ops.leaving_out``). A class's ``frac`` is its arithmetic over the measured
+bf16 peak (products and attention of the prompt step) or its bytes over the measured copy
+bandwidth (everything else), so that like kernels of the two models can be set side by side.
+One JSON line.
+"""
+
+from __future__ import annotations
+
+import json
+import tempfile
+from pathlib import Path
+
+PROMPTS, LENGTH, BATCH = 2, 1024, 8
+
+
+def mapuvik_config(width: int, heads: int, ff: int, repeats: int, vocab: int) -> dict:
+    head = width // heads
+    latent = {"type": "latent_attention", "mixer": {
+        "heads": heads, "dim": head, "rot_dim": head // 2, "vdim": head,
+        "kv_rank": 256 - head // 2,
+        "scale": (head + head // 2) ** -0.5, "mask": {"size": LENGTH},
+        "rot": {"base": 10000.0, "dims": head // 2}}}
+    mamba = {"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128,
+                                         "groups": 1, "conv": 4, "norm_groups": 1}}
+    memory_heads = max(1, width // 256)
+    mlstm = {"type": "mlstm", "mixer": {"heads": memory_heads, "dim": width // memory_heads,
+                                        "vdim": width // memory_heads, "gate_cap": 15.0}}
+    mlp = {"kind": "dense", "ff": ff}
+    layers = [{**kind, "mlp": mlp} for _ in range(repeats) for kind in (latent, mamba, mlstm)]
+    return {"architecture": "Mapuvik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": layers}
+
+
+def gpt2_config(width: int, heads: int, ff: int, layers: int, vocab: int) -> dict:
+    return {"architectures": ["GPT2LMHeadModel"], "n_layer": layers, "n_embd": width,
+            "n_head": heads, "n_inner": ff, "vocab_size": vocab, "n_positions": 2 * LENGTH,
+            "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new",
+            "scale_attn_by_inverse_layer_idx": False, "tie_word_embeddings": True}
+
+
+def _core(config: dict):
+    import torch
+
+    from ayaka_b200.config.engine import EngineConfig
+    from ayaka_b200.engine.core import EngineCore
+    from ayaka_b200.weights.random_init import random_state
+
+    state = random_state(config, 0, None, "bfloat16")
+    with tempfile.TemporaryDirectory() as folder:
+        (Path(folder) / "config.json").write_text(json.dumps(config))
+        core = EngineCore.from_config(
+            EngineConfig(model=folder, dtype="bfloat16", device="cuda:0", block_size=16,
+                         num_blocks=BATCH * (LENGTH + 64) // 16 + 1, max_running=BATCH,
+                         max_tokens_per_step=PROMPTS * LENGTH, max_context=LENGTH + 64),
+            tensors=state)
+    del state
+    torch.cuda.synchronize()
+    return core
+
+
+def _tokens(vocab: int, count: int, seed: int) -> list[int]:
+    import torch
+
+    return torch.randint(0, vocab, (count,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def _class_work(config: dict, rows: int, keys_per_row: float, decode: bool,
+                wanted: int) -> dict[str, dict]:
+    """Per kernel class of a step: FLOPs and bytes summed over the layers. ``keys_per_row``:
+    mean number of keys a row attends; ``wanted``: rows that reach the head."""
+    work: dict[str, dict] = {}
+
+    def add(name: str, flops: float, nbytes: float) -> None:
+        entry = work.setdefault(name, {"flops": 0.0, "bytes": 0.0})
+        entry["flops"] += flops
+        entry["bytes"] += nbytes
+
+    def product(n: int, k: int, out_bytes: int = 2, m: int = rows) -> None:
+        add(f"linear:{n}x{k}", 2.0 * m * n * k, n * k * 2 + m * (k * 2 + n * out_bytes))
+
+    if "n_embd" in config:
+        d, f, h = config["n_embd"], config["n_inner"], config["n_head"]
+        for _ in range(config["n_layer"]):
+            product(3 * d, d)
+            product(d, d, 4)
+            product(f, d)
+            product(d, f, 4)
+            add("attention", 4.0 * rows * keys_per_row * d, rows * keys_per_row * 2 * d * 2 / (
+                1 if decode else LENGTH / 8))
+            add("layer_norm", 0.0, 2 * rows * d * 6)
+        product(config["vocab_size"], d, 4, wanted)
+        return work
+    width = config["width"]
+    for layer in config["layers"]:
+        m = layer["mixer"]
+        if layer["mlp"]:
+            product(layer["mlp"]["ff"], width)
+            product(width, layer["mlp"]["ff"], 4)
+        add("rms_norm", 0.0, rows * width * 6)
+        if layer["type"] == "latent_attention":
+            H, dim, rot, vdim, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            product(H * (dim + rot) + rank + rot + H * vdim, width, 4)
+            product(width, H * vdim, 4)
+            add("latent_prepare", 0.0, rows * (H * (dim + rot) * 6 + (rank + rot) * 6))
+            add("head_linear", 2.0 * rows * H * rank * (dim + vdim),
+                H * rank * (dim + vdim) * 2 + rows * H * (dim + vdim + 2 * rank) * 2)
+            # every head scores rank + rot entries and sums rank entries of each key row; a
+            # decode step must read each request's rows once, whatever the number of heads
+            add("latent_attention", 2.0 * rows * keys_per_row * H * (2 * rank + rot),
+                rows * keys_per_row * (rank + rot) * 2 / (1 if decode else LENGTH / 8))
+        elif layer["type"] == "mamba2":
+            H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+            inner, channels = H * P, H * P + 2 * G * N
+            product(2 * inner + 2 * G * N + H, width, 4)
+            product(width, inner, 4)
+            add("causal_conv_silu", 2.0 * rows * channels * m["conv"], rows * channels * 8)
+            add("mamba2_scan", 6.0 * rows * H * N * P,
+                rows * (channels + H + inner) * 4 + (2 * H * N * P * 4) * (rows if decode else 2))
+            add("rms_norm", 0.0, rows * inner * 10)
+        else:
+            H, dim, P = m["heads"], m["dim"], m["vdim"]
+            product(2 * H * dim + 2 * H * P + 2 * H, width, 4)
+            product(width, H * P, 4)
+            add("mlstm_scan", 6.0 * rows * H * dim * P,
+                rows * (2 * H * dim + 2 * H * P) * 4 + (2 * H * dim * P * 4) * (
+                    rows if decode else 2))
+            add("rms_norm", 0.0, rows * H * P * 10)
+    product(config["vocab"], width, 4, wanted)
+    return work
+
+
+def _measure(config: dict, peak: dict) -> dict:
+    import torch
+
+    from bench import _timed_graph
+    from ayaka_b200.engine.runner import StepEntry
+    from ayaka_b200.kernels import ops
+
+    core = _core(config)
+    vocab = config.get("vocab") or config["vocab_size"]
+    model, runner, manager = core.model, core.runner, core.manager
+    tflops, gbs = peak["bf16_tflops"] * 1e12, peak["hbm_gbs"] * 1e9
+    out: dict[str, object] = {}
+
+    def forward_of(entries):  # the step's context, as the engine prepares it
+        for entry in entries:
+            assert manager.allocate(entry.request_id, len(entry.tokens))
+        step, want_rows, num_want = runner.prepare(entries)
+        return lambda: model.forward(step, runner.caches, want_rows, num_want)
+
+    def commit(entries) -> None:
+        for entry in entries:
+            manager.commit(entry.request_id, len(entry.tokens))
+
+    def classes(body, work, decode: bool, step_ms: float) -> dict:
+        found: dict[str, dict] = {}
+        if decode:
+            for name in work:
+                with ops.leaving_out({"attention": "attention_decode"}.get(name, name)):
+                    without = _timed_graph(body, 5)
+                found[name] = {"us": round(max(step_ms - without, 0.0) * 1000, 1)}
+        else:
+            filler = torch.empty(64 << 20, device="cuda")
+            for _ in range(2):
+                with ops.timed() as record:
+                    for _ in range(20):
+                        filler.zero_()  # the device is busy while the host queues the step
+                    body()
+                torch.cuda.synchronize()
+            for klass, pairs in record.items():
+                name = klass if klass in work else {"attention_prefill": "attention",
+                                                    "linear_kv": klass}.get(klass, klass)
+                if name in work:
+                    us = sum(start.elapsed_time(stop) for start, stop in pairs) * 1000
+                    found.setdefault(name, {"us": 0.0})["us"] += us
+            for name in found:
+                found[name]["us"] = round(found[name]["us"], 1)
+        for name, entry in found.items():
+            seconds = max(entry["us"], 1e-3) * 1e-6
+            by_flops = work[name]["flops"] / seconds / tflops
+            by_bytes = work[name]["bytes"] / seconds / gbs
+            tensor = not decode and (name.startswith("linear") or "attention" in name
+                                     or name == "head_linear")
+            entry["frac"] = round(by_flops if tensor else by_bytes, 4)
+            entry["of"] = "bf16_tflops" if tensor else "hbm_gbs"
+        return found
+
+    # ---- the prompt step
+    prompts = [StepEntry(f"p{i}", _tokens(vocab, LENGTH, i), (LENGTH - 1,))
+               for i in range(PROMPTS)]
+    native = ops.NATIVE_STEP
+    body = forward_of(prompts)
+    ms = _timed_graph(body, 5)
+    ops.NATIVE_STEP = False  # one Python call per kernel: where a class can be timed
+    try:
+        rows = PROMPTS * LENGTH
+        out["prefill"] = {"ms": round(ms, 3), "tok_s": round(rows * 1000.0 / ms, 1),
+                          "classes": classes(body, _class_work(config, rows, (LENGTH + 1) / 2,
+                                                               False, PROMPTS), False, ms)}
+        commit(prompts)
+        for i in range(PROMPTS, BATCH):  # the other requests of the decode batch
+            extra = [StepEntry(f"p{i}", _tokens(vocab, LENGTH, i), ())]
+            core.step(extra)
+        # ---- the decode step
+        ops.NATIVE_STEP = native
+        decodes = [StepEntry(f"p{i}", [7 + i], (0,)) for i in range(BATCH)]
+        body = forward_of(decodes)
+        ms = _timed_graph(body, 10)
+        ops.NATIVE_STEP = False
+        body_classes = forward_of(decodes)
+        out["decode"] = {"ms": round(ms, 4), "tok_s": round(BATCH * 1000.0 / ms, 1),
+                         "batch": BATCH, "context": LENGTH + 1,
+                         "classes": classes(body_classes, _class_work(
+                             config, BATCH, LENGTH + 1, True, BATCH), True,
+                             _timed_graph(body_classes, 10))}
+    finally:
+        ops.NATIVE_STEP = native
+    runner.check_device_flags()
+    del core
+    torch.cuda.empty_cache()
+    return out
+
+
+def run(sizes: str | None = None) -> dict:
+    from bench import peaks
+
+    peak, source = peaks()
+    table = {"1024": (1024, 16, 4096, 2), "2048": (2048, 16, 8192, 2)}
+    picked = [s for s in (sizes.split(",") if sizes else table) if s in table]
+    results = {}
+    for name in picked:
+        width, heads, ff, repeats = table[name]
+        results[name] = {
+            "layers": 3 * repeats, "width": width, "heads": heads, "ff": ff,
+            "mapuvik": _measure(mapuvik_config(width, heads, ff, repeats, 32000), peak),
+            "gpt2": _measure(gpt2_config(width, heads, ff, 3 * repeats, 32000), peak),
+        }
+    return {"metric": "Mapuvik beside GPT-2 of equal size: one 2,048-token prompt step and one "
+                      "decode step of 8 requests at context 1,025 (bf16, random weights)",
+            "peaks": {**{k: peak[k] for k in ("hbm_gbs", "bf16_tflops")}, "source": source},
+            "timing": "CUDA-graph replay of the model's forward, device time, best of 5 / 10",
+            "sizes": results}
