@@ -11,6 +11,8 @@
 // rows are taken in chunks: the chunk's inputs are brought to shared memory by all threads
 // (and the gates turned into factors there, one thread per row), then every thread walks the
 // chunk row by row.
+#include <initializer_list>
+
 #include "common.cuh"
 
 namespace ayk {
@@ -98,6 +100,46 @@ __global__ void conv_state_update_kernel(const float* __restrict__ in, int ld_in
 }
 
 // ---------------------------------------------------------------------------------------------
+// Staging of a chunk's inputs: asynchronous copies (16 bytes each where every address allows
+// it, else 4), all in flight at once, into one of two buffers, so that the copies of chunk
+// c + 1 travel while chunk c is walked.
+__device__ __forceinline__ void copy_async(float* dst, const float* src, int floats) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  if (floats == 4) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+  } else {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+  }
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// rows x width floats from rows `ld` apart into a dense tile; vec = 4 or 1 floats per copy
+__device__ __forceinline__ void stage_tile(float* dst, const float* src, long long ld, int rows,
+                                           int width, int vec) {
+  const int per_row = width / vec;
+  for (int idx = threadIdx.x; idx < rows * per_row; idx += SCAN_THREADS) {
+    const int i = idx / per_row, j = (idx % per_row) * vec;
+    copy_async(dst + (size_t)i * width + j, src + (size_t)i * ld + j, vec);
+  }
+}
+// the CTA's SCAN_COLS columns (from column p0 of a head of P columns; zeros beyond P)
+__device__ __forceinline__ void stage_columns(float* dst, const float* src, long long ld,
+                                              int rows, int p0, int P, int vec) {
+  const int per_row = SCAN_COLS / vec;
+  for (int idx = threadIdx.x; idx < rows * per_row; idx += SCAN_THREADS) {
+    const int i = idx / per_row, j = (idx % per_row) * vec;
+    float* to = dst + i * SCAN_COLS + j;
+    if (p0 + j < P) {  // (with vec 4, P is a multiple of 4: a group is inside or outside)
+      copy_async(to, src + (size_t)i * ld + p0 + j, vec);
+    } else {
+      for (int e = 0; e < vec; ++e) to[e] = 0.f;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Mamba-2: per head h (group g = h / (heads / groups)), dt = softplus(dt_raw + dt_bias),
 //   S <- exp(-exp(A_log) dt) S + dt B x^T,   y = S^T C + D x,    S: [N x P].
 // xbc rows: [ x: heads x P | B: groups x N | C: groups x N ] (after convolution and silu).
@@ -110,13 +152,9 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __res
                    float* __restrict__ state, long long state_stride,
                    const int* __restrict__ row_start, const int* __restrict__ state_slot,
                    float* __restrict__ y, int ld_y, int heads, int groups, int N, int P,
-                   int chunk) {
-  extern __shared__ float scan_smem[];
-  float* b_s = scan_smem;                 // [chunk][N]
-  float* c_s = b_s + (size_t)chunk * N;   // [chunk][N]
-  float* x_s = c_s + (size_t)chunk * N;   // [chunk][SCAN_COLS]
-  float* dt_s = x_s + chunk * SCAN_COLS;  // [chunk]
-  float* decay_s = dt_s + chunk;          // [chunk]
+                   int chunk, int vec) {
+  extern __shared__ __align__(16) float scan_smem[];
+  const int stage_floats = chunk * (2 * N + SCAN_COLS + 4);
   pdl_launch_dependents();
   const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * SCAN_COLS;
   const int col = threadIdx.x / SCAN_LANES, part = threadIdx.x % SCAN_LANES;
@@ -133,22 +171,37 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __res
     const int n = part + SCAN_LANES * k;
     s[k] = (live && n < N) ? mine[(size_t)n * P + p] : 0.f;
   }
-  for (int t0 = 0; t0 < rows; t0 += chunk) {
-    const int count = min(chunk, rows - t0);
-    __syncthreads();  // the chunk before has been walked
+  const int chunks = (rows + chunk - 1) / chunk;
+  auto stage = [&](int c) {
+    float* at = scan_smem + (size_t)(c & 1) * stage_floats;
+    const int t0 = c * chunk, count = min(chunk, rows - t0);
     const float* first = xbc + (size_t)(r0 + t0) * ld_xbc;
-    for (int idx = threadIdx.x; idx < count * N; idx += SCAN_THREADS) {
-      const int i = idx / N, n = idx % N;
-      const float* row = first + (size_t)i * ld_xbc + inner + g * N;
-      b_s[idx] = row[n];
-      c_s[idx] = row[groups * N + n];
+    stage_tile(at, first + inner + g * N, ld_xbc, count, N, vec);                          // B
+    stage_tile(at + (size_t)chunk * N, first + inner + (groups + g) * N, ld_xbc, count, N, vec);
+    stage_columns(at + (size_t)2 * chunk * N, first + h * P, ld_xbc, count, p0, P, vec);   // x
+    for (int i = threadIdx.x; i < count; i += SCAN_THREADS) {                              // dt
+      copy_async(at + 2 * chunk * N + chunk * SCAN_COLS + i,
+                 dt_raw + (size_t)(r0 + t0 + i) * ld_dt + h, 1);
     }
-    for (int idx = threadIdx.x; idx < count * SCAN_COLS; idx += SCAN_THREADS) {
-      const int i = idx / SCAN_COLS, cc = idx % SCAN_COLS;
-      x_s[idx] = p0 + cc < P ? first[(size_t)i * ld_xbc + h * P + p0 + cc] : 0.f;
+    copy_commit();
+  };
+  stage(0);
+  for (int c = 0; c < chunks; ++c) {
+    if (c + 1 < chunks) {
+      stage(c + 1);
+      copy_wait<1>();
+    } else {
+      copy_wait<0>();
     }
+    __syncthreads();
+    float* b_s = scan_smem + (size_t)(c & 1) * stage_floats;
+    float* c_s = b_s + (size_t)chunk * N;
+    float* x_s = c_s + (size_t)chunk * N;
+    float* dt_s = x_s + chunk * SCAN_COLS;   // raw, then the step size
+    float* decay_s = dt_s + chunk;
+    const int t0 = c * chunk, count = min(chunk, rows - t0);
     for (int i = threadIdx.x; i < count; i += SCAN_THREADS) {
-      const float dt = softplus_f(dt_raw[(size_t)(r0 + t0 + i) * ld_dt + h] + bias);
+      const float dt = softplus_f(dt_s[i] + bias);
       dt_s[i] = dt;
       decay_s[i] = expf(rate * dt);
     }
@@ -170,6 +223,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __res
       acc = group_sum8(acc);
       if (part == 0 && live) y[(size_t)(r0 + t0 + i) * ld_y + h * P + p] = acc + d_skip * xv;
     }
+    __syncthreads();  // the buffer is staged again two chunks on
   }
 #pragma unroll
   for (int k = 0; k < RN; ++k) {
@@ -183,7 +237,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __res
 // f = logsigmoid(cap tanh((f_raw + b_f) / cap)) and a running maximum m (0 at the start):
 //   m' = max(f + m, i);  keep = e^(f + m - m'), take = e^(i - m');
 //   S <- keep S + take k v^T;  n <- keep n + take k;
-//   out = S^T q / (max(|n . q|, e^(-m')) + 1e-6),   q already times dim^(-1/2).
+//   out = S^T q / (max(|n . q|, e^(-m')) + 1e-6),   q times dim^(-1/2).
 // proj rows: [ q: H x dim | k: H x dim | v: H x P | (gate, not read here) | i_raw: H | f_raw: H ]
 // at the given offsets. State of a slot: S [H][dim][P]; then, once per tile of SCAN_COLS
 // columns so that no CTA reads what another writes, n [H][tiles][dim] and m [H][tiles].
@@ -193,14 +247,10 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
                   int i_offset, int f_offset, const float* __restrict__ gate_bias, float cap,
                   float* __restrict__ state, long long state_stride,
                   const int* __restrict__ row_start, const int* __restrict__ state_slot,
-                  float* __restrict__ out, int ld_out, int heads, int dim, int P, int chunk) {
-  extern __shared__ float scan_smem[];
-  float* q_s = scan_smem;                   // [chunk][dim]
-  float* k_s = q_s + (size_t)chunk * dim;   // [chunk][dim]
-  float* v_s = k_s + (size_t)chunk * dim;   // [chunk][SCAN_COLS]
-  float* keep_s = v_s + chunk * SCAN_COLS;  // [chunk]: log gate f, then the factor
-  float* take_s = keep_s + chunk;           // [chunk]: log gate i, then the factor
-  float* floor_s = take_s + chunk;          // [chunk]: e^(-m')
+                  float* __restrict__ out, int ld_out, int heads, int dim, int P, int chunk,
+                  int vec) {
+  extern __shared__ __align__(16) float scan_smem[];
+  const int stage_floats = chunk * (2 * dim + SCAN_COLS + 4);
   __shared__ float m_run;
   pdl_launch_dependents();
   const int h = blockIdx.x, b = blockIdx.y, tile = blockIdx.z, tiles = gridDim.z;
@@ -225,24 +275,42 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
     nrm[k] = n < dim ? norm_mine[n] : 0.f;
   }
   if (threadIdx.x == 0) m_run = *max_mine;
-  for (int t0 = 0; t0 < rows; t0 += chunk) {
-    const int count = min(chunk, rows - t0);
-    __syncthreads();
+  const int chunks = (rows + chunk - 1) / chunk;
+  auto stage = [&](int c) {
+    float* at = scan_smem + (size_t)(c & 1) * stage_floats;
+    const int t0 = c * chunk, count = min(chunk, rows - t0);
     const float* first = proj + (size_t)(r0 + t0) * ld_proj;
-    for (int idx = threadIdx.x; idx < count * dim; idx += SCAN_THREADS) {
-      const int i = idx / dim, n = idx % dim;
-      const float* row = first + (size_t)i * ld_proj + h * dim;
-      q_s[idx] = row[n] * q_scale;
-      k_s[idx] = row[k_offset + n];
+    stage_tile(at, first + h * dim, ld_proj, count, dim, vec);                               // q
+    stage_tile(at + (size_t)chunk * dim, first + k_offset + h * dim, ld_proj, count, dim, vec);
+    stage_columns(at + (size_t)2 * chunk * dim, first + v_offset + h * P, ld_proj, count, p0, P,
+                  vec);                                                                     // v
+    float* gates = at + 2 * chunk * dim + chunk * SCAN_COLS;
+    for (int i = threadIdx.x; i < 2 * count; i += SCAN_THREADS) {
+      const int row = i >> 1;
+      copy_async(gates + (i & 1) * chunk + row,
+                 first + (size_t)row * ld_proj + ((i & 1) ? i_offset : f_offset) + h, 1);
     }
-    for (int idx = threadIdx.x; idx < count * SCAN_COLS; idx += SCAN_THREADS) {
-      const int i = idx / SCAN_COLS, cc = idx % SCAN_COLS;
-      v_s[idx] = p0 + cc < P ? first[(size_t)i * ld_proj + v_offset + h * P + p0 + cc] : 0.f;
+    copy_commit();
+  };
+  stage(0);
+  for (int c = 0; c < chunks; ++c) {
+    if (c + 1 < chunks) {
+      stage(c + 1);
+      copy_wait<1>();
+    } else {
+      copy_wait<0>();
     }
+    __syncthreads();
+    float* q_s = scan_smem + (size_t)(c & 1) * stage_floats;
+    float* k_s = q_s + (size_t)chunk * dim;
+    float* v_s = k_s + (size_t)chunk * dim;
+    float* keep_s = v_s + chunk * SCAN_COLS;  // raw forget gate, log gate f, then the factor
+    float* take_s = keep_s + chunk;           // raw input gate, log gate i, then the factor
+    float* floor_s = take_s + chunk;          // e^(-m')
+    const int t0 = c * chunk, count = min(chunk, rows - t0);
     for (int i = threadIdx.x; i < count; i += SCAN_THREADS) {
-      const float* row = first + (size_t)i * ld_proj;
-      take_s[i] = cap * tanhf((row[i_offset + h] + bias_i) / cap);
-      keep_s[i] = log_sigmoid_f(cap * tanhf((row[f_offset + h] + bias_f) / cap));
+      take_s[i] = cap * tanhf((take_s[i] + bias_i) / cap);
+      keep_s[i] = log_sigmoid_f(cap * tanhf((keep_s[i] + bias_f) / cap));
     }
     __syncthreads();
     if (threadIdx.x == 0) {  // the scalar recurrence of the maximum, in row order
@@ -275,15 +343,15 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
           dot = fmaf(nrm[k], qq, dot);
         }
       }
-      acc = group_sum8(acc);
-      dot = group_sum8(dot);
+      acc = group_sum8(acc) * q_scale;
+      dot = group_sum8(dot) * q_scale;
       if (part == 0 && live) {
         out[(size_t)(r0 + t0 + i) * ld_out + h * P + p] =
             acc / (fmaxf(fabsf(dot), floor_s[i]) + 1e-6f);
       }
     }
+    __syncthreads();  // the buffer is staged again two chunks on
   }
-  __syncthreads();
 #pragma unroll
   for (int k = 0; k < RN; ++k) {
     const int n = part + SCAN_LANES * k;
@@ -293,7 +361,18 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
   if (threadIdx.x == 0) *max_mine = m_run;
 }
 
-inline int scan_chunk(int n) { return n <= 128 ? 32 : 16; }
+// rows of a chunk: two buffers of chunk * (2 n + SCAN_COLS + 4) floats stay under 48 KB
+inline int scan_chunk(int n) { return n <= 64 ? 32 : (n <= 128 ? 16 : 8); }
+inline size_t scan_smem_bytes(int chunk, int n) {
+  return (size_t)2 * chunk * (2 * n + SCAN_COLS + 4) * sizeof(float);
+}
+// 16-byte copies when every staged address is a multiple of 16 bytes, else 4-byte ones
+inline int scan_vec(const float* base, long long ld, int n, int P,
+                    std::initializer_list<long long> offsets) {
+  bool ok = ((uintptr_t)base % 16) == 0 && ld % 4 == 0 && n % 4 == 0 && P % 4 == 0;
+  for (long long o : offsets) ok = ok && o % 4 == 0;
+  return ok ? 4 : 1;
+}
 
 }  // namespace ayk
 
@@ -345,13 +424,14 @@ AYK_API int ayk_mamba2_scan(const float* xbc, int ld_xbc, const float* dt_raw, i
   }
   if (N > SCAN_LANES * 32 || (P + SCAN_COLS - 1) / SCAN_COLS > 65535) return AYK_TOO_LARGE;
   const int chunk = scan_chunk(N);
-  const size_t smem = ((size_t)chunk * (2 * N + SCAN_COLS + 2)) * sizeof(float);
+  const size_t smem = scan_smem_bytes(chunk, N);
+  const int vec = scan_vec(xbc, ld_xbc, N, P, {(long long)heads * P});
   const dim3 grid(heads, requests, (P + SCAN_COLS - 1) / SCAN_COLS);
 #define AYK_MAMBA(RN)                                                                          \
   return launch_kernel(mamba2_scan_kernel<RN>, grid, dim3(SCAN_THREADS), smem,                 \
                        (cudaStream_t)stream, 1, xbc, ld_xbc, dt_raw, ld_dt, dt_bias, a_log,    \
                        skip, state, state_stride, row_start, state_slot, y, ld_y, heads,       \
-                       groups, N, P, chunk)
+                       groups, N, P, chunk, vec)
   if (N <= SCAN_LANES * 2) AYK_MAMBA(2);
   if (N <= SCAN_LANES * 4) AYK_MAMBA(4);
   if (N <= SCAN_LANES * 8) AYK_MAMBA(8);
@@ -376,13 +456,14 @@ AYK_API int ayk_mlstm_scan(const float* proj, int ld_proj, int k_offset, int v_o
   }
   if (dim > SCAN_LANES * 32 || tiles > 65535) return AYK_TOO_LARGE;
   const int chunk = scan_chunk(dim);
-  const size_t smem = ((size_t)chunk * (2 * dim + SCAN_COLS + 3)) * sizeof(float);
+  const size_t smem = scan_smem_bytes(chunk, dim);
+  const int vec = scan_vec(proj, ld_proj, dim, P, {k_offset, v_offset});
   const dim3 grid(heads, requests, tiles);
 #define AYK_MLSTM(RN)                                                                          \
   return launch_kernel(mlstm_scan_kernel<RN>, grid, dim3(SCAN_THREADS), smem,                  \
                        (cudaStream_t)stream, 1, proj, ld_proj, k_offset, v_offset, i_offset,   \
                        f_offset, gate_bias, cap, state, state_stride, row_start, state_slot,   \
-                       out, ld_out, heads, dim, P, chunk)
+                       out, ld_out, heads, dim, P, chunk, vec)
   if (dim <= SCAN_LANES * 2) AYK_MLSTM(2);
   if (dim <= SCAN_LANES * 4) AYK_MLSTM(4);
   if (dim <= SCAN_LANES * 8) AYK_MLSTM(8);
