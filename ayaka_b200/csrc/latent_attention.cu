@@ -88,63 +88,70 @@ __global__ void latent_prepare_kernel(const float* __restrict__ proj, int ld_pro
 // order of i whatever the batch. W_h(i, j) sits at w + h * w_head + i * w_in + j * w_out, so a
 // head's matrix is used as stored ([in, out] rows: w_in = cols, w_out = 1) or transposed
 // ([out, in] rows: w_in = 1, w_out = cols). With `gate` (fp32 [n][h * J + j]) the result is
-// multiplied by sigmoid(gate). Tiles of 32 rows x 64 columns, 16 of the inner dimension at a
-// time through shared memory; a thread owns 2 x 4 results.
-constexpr int HL_BM = 32, HL_BN = 64, HL_BK = 16;
+// multiplied by sigmoid(gate). Tiles go through shared memory a slice of the inner dimension
+// at a time.
+constexpr int HL_BN = 64;
 
-template <typename T>
+// A CTA of 256 threads computes (256 / (HL_BN / TN)) * TM rows x HL_BN columns, BK of the
+// inner dimension at a time: <2, 4, 16> is 32 rows x 64 columns for prompt portions; <1, 2, 64>
+// is 8 rows x 64 columns in a quarter of the turns, for the few rows of a decode step, where
+// what counts is the number of trips to memory, not the arithmetic.
+template <typename T, int TM, int TN, int BK>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(const T* __restrict__ a, int ld_a, int a_head, const T* __restrict__ w,
                    long long w_head, int w_in, int w_out, const float* __restrict__ gate,
                    int ld_gate, T* __restrict__ out, int ld_out, int out_head, int rows, int I,
                    int J) {
-  __shared__ float a_s[HL_BK][HL_BM + 1];
-  __shared__ float w_s[HL_BK][HL_BN + 1];
+  constexpr int TX = HL_BN / TN, TY = 256 / TX, BM = TY * TM;
+  __shared__ float a_s[BK][BM + 1];
+  __shared__ float w_s[BK][HL_BN + 1];
   pdl_launch_dependents();
-  const int h = blockIdx.z, m0 = blockIdx.x * HL_BM, n0 = blockIdx.y * HL_BN;
-  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  const int h = blockIdx.z, m0 = blockIdx.x * BM, n0 = blockIdx.y * HL_BN;
+  const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
   const T* wh = w + (size_t)h * w_head;
   pdl_wait_for(a, gate);
   const T* ah = a + (size_t)h * a_head;
-  float acc[2][4] = {};
-  for (int k0 = 0; k0 < I; k0 += HL_BK) {
-    for (int idx = threadIdx.x; idx < HL_BK * HL_BM; idx += 256) {
-      const int kk = idx % HL_BK, mm = idx / HL_BK;
+  float acc[TM][TN] = {};
+  for (int k0 = 0; k0 < I; k0 += BK) {
+    for (int idx = threadIdx.x; idx < BK * BM; idx += 256) {
+      const int kk = idx % BK, mm = idx / BK;
       const int m = m0 + mm, k = k0 + kk;
       a_s[kk][mm] = (m < rows && k < I) ? ldf(ah + (size_t)m * ld_a + k) : 0.f;
     }
-    for (int idx = threadIdx.x; idx < HL_BK * HL_BN; idx += 256) {
+    for (int idx = threadIdx.x; idx < BK * HL_BN; idx += 256) {
       int kk, nn;
       if (w_out == 1) {  // consecutive threads along the unit stride
         nn = idx % HL_BN;
         kk = idx / HL_BN;
       } else {
-        kk = idx % HL_BK;
-        nn = idx / HL_BK;
+        kk = idx % BK;
+        nn = idx / BK;
       }
       const int n = n0 + nn, k = k0 + kk;
       w_s[kk][nn] = (n < J && k < I) ? ldf(wh + (size_t)k * w_in + (size_t)n * w_out) : 0.f;
     }
     __syncthreads();
 #pragma unroll
-    for (int kk = 0; kk < HL_BK; ++kk) {
-      const float a0 = a_s[kk][ty * 2], a1 = a_s[kk][ty * 2 + 1];
+    for (int kk = 0; kk < BK; ++kk) {
+      float av[TM];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float wv = w_s[kk][tx * 4 + c];
-        acc[0][c] = fmaf(a0, wv, acc[0][c]);
-        acc[1][c] = fmaf(a1, wv, acc[1][c]);
+      for (int r = 0; r < TM; ++r) av[r] = a_s[kk][ty * TM + r];
+#pragma unroll
+      for (int c = 0; c < TN; ++c) {
+        const float wv = w_s[kk][tx * TN + c];
+#pragma unroll
+        for (int r = 0; r < TM; ++r) acc[r][c] = fmaf(av[r], wv, acc[r][c]);
       }
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int m = m0 + ty * 2 + r;
+  for (int r = 0; r < TM; ++r) {
+    const int m = m0 + ty * TM + r;
     if (m >= rows) continue;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const int n = n0 + tx * 4 + c;
+    for (int c = 0; c < TN; ++c) {
+      const int n = n0 + tx * TN + c;
       if (n >= J) continue;
       float v = acc[r][c];
       if (gate != nullptr) {
@@ -154,6 +161,22 @@ head_linear_kernel(const T* __restrict__ a, int ld_a, int a_head, const T* __res
       stf(out + (size_t)m * ld_out + (size_t)h * out_head + n, v);
     }
   }
+}
+
+template <typename T>
+int head_linear(const void* a, int ld_a, int a_head, const void* w, long long w_head, int w_in,
+                int w_out, const float* gate, int ld_gate, void* out, int ld_out, int out_head,
+                int rows, int heads, int I, int J, cudaStream_t s) {
+  const int tiles = (J + HL_BN - 1) / HL_BN;
+  if (tiles > 65535) return AYK_TOO_LARGE;
+  if (rows <= 16) {
+    return launch_kernel(head_linear_kernel<T, 1, 2, 64>, dim3((rows + 7) / 8, tiles, heads),
+                         dim3(256), 0, s, 1, (const T*)a, ld_a, a_head, (const T*)w, w_head,
+                         w_in, w_out, gate, ld_gate, (T*)out, ld_out, out_head, rows, I, J);
+  }
+  return launch_kernel(head_linear_kernel<T, 2, 4, 16>, dim3((rows + 31) / 32, tiles, heads),
+                       dim3(256), 0, s, 1, (const T*)a, ld_a, a_head, (const T*)w, w_head, w_in,
+                       w_out, gate, ld_gate, (T*)out, ld_out, out_head, rows, I, J);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -272,6 +295,169 @@ latent_attention_kernel(const T* __restrict__ qa, int ld_qa, const T* __restrict
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same attention for steps of single rows (decode), where the time is the rows' trip from
+// memory: a CTA takes one row and one share of its keys for ALL heads, so a latent row is
+// fetched once whatever the number of heads. Tiles of 32 keys travel by 16-byte asynchronous
+// copies into two padded shared-memory buffers (row stride + 16 bytes: a quarter warp's
+// 16-byte reads of eight different rows fall on different banks); warp w takes heads w, w + 8,
+// ...: lane j scores key j of the tile, the warp keeps the head's running maximum and sum, then
+// lane l adds up entries 8 l .. 8 l + 7 of the rows. Every share writes (maximum, sum, weighted
+// rows) to scratch and a second launch merges the shares in share order. The walk over a
+// row's keys is cut at multiples of 32 counted from key 0, by position alone.
+constexpr int LD_WARPS = 8, LD_HEADS = 4;  // heads per warp at most: 32 heads per CTA
+
+__device__ __forceinline__ void la_copy16(void* dst, const void* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(LD_WARPS * 32)
+latent_decode_kernel(const T* __restrict__ qa, int ld_qa, const T* __restrict__ pages,
+                     const int* __restrict__ block_table, int table_stride,
+                     const int* __restrict__ request_of_row, const int* __restrict__ positions,
+                     float* __restrict__ partial, int num_heads, int rank, int key_dim,
+                     int page_size, float scale, int window, int splits) {
+  extern __shared__ __align__(16) unsigned char ld_smem[];
+  constexpr int PER16 = 16 / sizeof(T);          // elements of a 16-byte piece
+  const int row_elems = key_dim + PER16;         // padded row
+  T* tile_s = reinterpret_cast<T*>(ld_smem);     // [2][32][row_elems]
+  float* q_s = reinterpret_cast<float*>(ld_smem + (size_t)2 * 32 * row_elems * sizeof(T));
+  __shared__ float w_s[LD_WARPS][32];
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x, split = blockIdx.y, head0 = blockIdx.z * LD_WARPS * LD_HEADS;
+  const int heads_here = min(num_heads - head0, LD_WARPS * LD_HEADS);
+  const int b = request_of_row[row], p = positions[row];
+  pdl_wait_for(qa, pages);
+  float* mine = partial + (((size_t)row * num_heads + head0) * splits + split) * (rank + 2);
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  // tiles of 32 keys from a multiple of 32; this share's tiles
+  const int first_tile = lo / 32, tiles = b < 0 ? 0 : p / 32 - first_tile + 1;
+  const int per = (tiles + splits - 1) / splits;
+  const int t_begin = first_tile + split * per, t_end = min(first_tile + tiles, t_begin + per);
+  for (int idx = threadIdx.x; idx < heads_here * key_dim; idx += LD_WARPS * 32) {
+    const int h = idx / key_dim, d = idx % key_dim;
+    q_s[idx] = ldf(qa + (size_t)row * ld_qa + (size_t)(head0 + h) * key_dim + d) * scale;
+  }
+  const int* table = block_table + (size_t)max(b, 0) * table_stride;
+  const int pieces = key_dim / PER16;
+  auto stage = [&](int tile, int buffer) {
+    T* at = tile_s + (size_t)buffer * 32 * row_elems;
+    for (int idx = threadIdx.x; idx < 32 * pieces; idx += LD_WARPS * 32) {
+      const int j = idx / pieces, c = idx % pieces, t = tile * 32 + j;
+      if (t >= lo && t <= p) {
+        const T* src = pages + ((size_t)table[t / page_size] * page_size + t % page_size) * key_dim;
+        la_copy16(at + (size_t)j * row_elems + c * PER16, src + c * PER16);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float m[LD_HEADS], l[LD_HEADS], acc[LD_HEADS][8];
+#pragma unroll
+  for (int u = 0; u < LD_HEADS; ++u) {
+    m[u] = -INFINITY;
+    l[u] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+  }
+  if (t_begin < t_end) stage(t_begin, 0);
+  for (int tile = t_begin; tile < t_end; ++tile) {
+    const int buffer = (tile - t_begin) & 1;
+    if (tile + 1 < t_end) {
+      stage(tile + 1, buffer ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const T* at = tile_s + (size_t)buffer * 32 * row_elems;
+    const int t = tile * 32 + lane;
+    const bool valid = t >= lo && t <= p;
+    const int count = min(32, p - tile * 32 + 1);
+#pragma unroll
+    for (int u = 0; u < LD_HEADS; ++u) {
+      const int h = warp + LD_WARPS * u;
+      if (h >= heads_here) break;
+      const float* q = q_s + (size_t)h * key_dim;
+      float score = -INFINITY;
+      if (valid) {
+        const T* key = at + (size_t)lane * row_elems;
+        float dot = 0.f;
+        for (int d = 0; d < key_dim; d += 8) {
+          float kv[8];
+          Chunk8<T>::load(key + d, kv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dot = fmaf(q[d + e], kv[e], dot);
+        }
+        score = dot;
+      }
+      const float m_new = fmaxf(m[u], warp_max(score));
+      const float wgt = valid ? expf(score - m_new) : 0.f;
+      const float corr = expf(m[u] - m_new);
+      l[u] = l[u] * corr + warp_sum(wgt);
+      m[u] = m_new;
+      __syncwarp();
+      w_s[warp][lane] = wgt;
+      __syncwarp();
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] *= corr;
+      if (lane * 8 < rank) {
+        for (int j = 0; j < count; ++j) {
+          const float wj = w_s[warp][j];
+          if (wj == 0.f) continue;  // (also every key before the window)
+          float vv[8];
+          Chunk8<T>::load(at + (size_t)j * row_elems + lane * 8, vv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[u][e] = fmaf(wj, vv[e], acc[u][e]);
+        }
+      }
+    }
+    __syncthreads();  // the buffer is staged again at the next turn
+  }
+#pragma unroll
+  for (int u = 0; u < LD_HEADS; ++u) {
+    const int h = warp + LD_WARPS * u;
+    if (h >= heads_here) break;
+    float* to = mine + (size_t)h * splits * (rank + 2);
+    if (lane == 0) {
+      to[0] = m[u];
+      to[1] = l[u];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      if (lane * 8 + e < rank) to[2 + lane * 8 + e] = acc[u][e];
+    }
+  }
+}
+
+template <typename T>
+__global__ void latent_decode_merge_kernel(const float* __restrict__ partial,
+                                           T* __restrict__ out, int ld_out, int out_head,
+                                           int num_heads, int rank, int splits) {
+  pdl_launch_dependents();
+  const int row = blockIdx.x, head = blockIdx.y;
+  pdl_wait_for(partial);
+  const float* from = partial + ((size_t)row * num_heads + head) * splits * (rank + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, from[(size_t)s * (rank + 2)]);
+  float l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* share = from + (size_t)s * (rank + 2);
+    if (share[1] > 0.f) l += share[1] * expf(share[0] - m);
+  }
+  T* dst = out + (size_t)row * ld_out + (size_t)head * out_head;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* share = from + (size_t)s * (rank + 2);
+      if (share[1] > 0.f) v += share[2 + d] * expf(share[0] - m);
+    }
+    stf(dst + d, l > 0.f ? v / l : 0.f);
+  }
+}
+
 template <typename T>
 int latent_attention(const void* qa, int ld_qa, const void* pages, const int* block_table,
                      int table_stride, const int* request_of_row, const int* positions, void* out,
@@ -346,18 +532,13 @@ AYK_API int ayk_head_linear(const void* a, int ld_a, int a_head, const void* w, 
     return AYK_BAD_ARGUMENT;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  const dim3 grid((rows + HL_BM - 1) / HL_BM, (J + HL_BN - 1) / HL_BN, heads);
-  if (grid.y > 65535) return AYK_TOO_LARGE;
   if (type == 0) {
-    return launch_kernel(head_linear_kernel<float>, grid, dim3(256), 0, s, 1, (const float*)a,
-                         ld_a, a_head, (const float*)w, w_head, w_in, w_out, gate, ld_gate,
-                         (float*)out, ld_out, out_head, rows, I, J);
+    return head_linear<float>(a, ld_a, a_head, w, w_head, w_in, w_out, gate, ld_gate, out, ld_out,
+                              out_head, rows, heads, I, J, s);
   }
   if (type == 1) {
-    return launch_kernel(head_linear_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, 1,
-                         (const __nv_bfloat16*)a, ld_a, a_head, (const __nv_bfloat16*)w, w_head,
-                         w_in, w_out, gate, ld_gate, (__nv_bfloat16*)out, ld_out, out_head, rows,
-                         I, J);
+    return head_linear<__nv_bfloat16>(a, ld_a, a_head, w, w_head, w_in, w_out, gate, ld_gate, out,
+                                      ld_out, out_head, rows, heads, I, J, s);
   }
   return AYK_BAD_ARGUMENT;
 }
@@ -388,4 +569,60 @@ AYK_API int ayk_latent_attention(const void* qa, int ld_qa, const void* pages,
                                            rank, rot, page_size, scale, window, s);
   }
   return AYK_BAD_ARGUMENT;
+}
+
+// Attention over latent pages for steps of single rows, every head of a row in one CTA (see
+// latent_decode_kernel). `partial`: rows * heads * splits * (rank + 2) floats of scratch.
+// out rows hold the heads `out_head` entries apart. Refused (AYK_NOT_TAKEN, nothing ran) for
+// sizes it does not take: rows of the cache that are no multiple of 8 entries or longer than
+// 320, a rank over 256.
+AYK_API int ayk_latent_decode(const void* qa, int ld_qa, const void* pages,
+                              const int* block_table, int table_stride,
+                              const int* request_of_row, const int* positions, float* partial,
+                              void* out, int ld_out, int out_head, int rows, int num_heads,
+                              int rank, int rot, int page_size, float scale, int window,
+                              int splits, int type, void* stream) {
+  using namespace ayk;
+  if (rows == 0) return AYK_OK;
+  const int key_dim = rank + rot;
+  if (rows < 0 || num_heads < 1 || rank < 1 || rot < 0 || page_size < 1 || window < 0 ||
+      splits < 1 || splits > 65535 || qa == nullptr || pages == nullptr ||
+      block_table == nullptr || request_of_row == nullptr || positions == nullptr ||
+      partial == nullptr || out == nullptr || ld_qa < num_heads * key_dim || out_head < rank ||
+      (type != 0 && type != 1)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (key_dim % 8 || key_dim > 320 || rank > 256 || ((uintptr_t)pages % 16)) return AYK_NOT_TAKEN;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int elem = type == 0 ? 4 : 2;
+  const int group = LD_WARPS * LD_HEADS;
+  const size_t smem = (size_t)2 * 32 * (key_dim + 16 / elem) * elem +
+                      (size_t)(num_heads < group ? num_heads : group) * key_dim * sizeof(float);
+  const dim3 grid(rows, splits, (num_heads + group - 1) / group);
+  int status;
+  if (type == 0) {
+    static const bool allowed = (cudaFuncSetAttribute(
+        latent_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024), true);
+    (void)allowed;
+    status = launch_kernel(latent_decode_kernel<float>, grid, dim3(LD_WARPS * 32), smem, s, 1,
+                           (const float*)qa, ld_qa, (const float*)pages, block_table,
+                           table_stride, request_of_row, positions, partial, num_heads, rank,
+                           key_dim, page_size, scale, window, splits);
+    if (status != AYK_OK) return status;
+    return launch_kernel(latent_decode_merge_kernel<float>, dim3(rows, num_heads), dim3(128), 0,
+                         s, 1, (const float*)partial, (float*)out, ld_out, out_head, num_heads,
+                         rank, splits);
+  }
+  static const bool allowed = (cudaFuncSetAttribute(
+      latent_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      160 * 1024), true);
+  (void)allowed;
+  status = launch_kernel(latent_decode_kernel<__nv_bfloat16>, grid, dim3(LD_WARPS * 32), smem, s,
+                         1, (const __nv_bfloat16*)qa, ld_qa, (const __nv_bfloat16*)pages,
+                         block_table, table_stride, request_of_row, positions, partial, num_heads,
+                         rank, key_dim, page_size, scale, window, splits);
+  if (status != AYK_OK) return status;
+  return launch_kernel(latent_decode_merge_kernel<__nv_bfloat16>, dim3(rows, num_heads),
+                       dim3(128), 0, s, 1, (const float*)partial, (__nv_bfloat16*)out, ld_out,
+                       out_head, num_heads, rank, splits);
 }

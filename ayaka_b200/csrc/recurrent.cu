@@ -6,8 +6,10 @@
 //
 // Both recurrences have the shape S_t = a_t S_(t-1) + b_t k_t v_t^T, y_t = S_t^T q_t with S
 // [n x p] per head, so the p columns of S never mix: a CTA owns one (head, request, tile of
-// SCAN_COLS columns); a column's n entries are spread over SCAN_LANES neighbouring lanes
-// (entry n on lane n % SCAN_LANES), which add up their shares of y with three shuffles. The
+// SCAN_COLS columns); a column's n entries are spread over LANES neighbouring lanes (8, 16 or
+// a whole warp, by the size of n: entry n on lane n % LANES, so that a thread holds at most
+// 8 entries and a device has thousands of warps to run), which add up their shares of y with
+// shuffles. A column is kept with its n entries side by side ([head][p][n]). The
 // rows are taken in chunks: the chunk's inputs are brought to shared memory by all threads
 // (and the gates turned into factors there, one thread per row), then every thread walks the
 // chunk row by row.
@@ -18,14 +20,13 @@
 namespace ayk {
 
 constexpr int SCAN_COLS = 16;   // columns of the state per CTA
-constexpr int SCAN_LANES = 8;   // lanes that share a column
-constexpr int SCAN_THREADS = SCAN_COLS * SCAN_LANES;
+constexpr int SCAN_MAX_N = 256;  // entries of a column: 32 lanes x 8
 constexpr int CONV_MAX_TAPS = 16;
+constexpr int SCAN_STAGES = 4;  // buffers of staged chunks: three travel while one is walked
 
-__device__ __forceinline__ float group_sum8(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 1);
-  v += __shfl_xor_sync(0xffffffffu, v, 2);
-  v += __shfl_xor_sync(0xffffffffu, v, 4);
+template <int LANES> __device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = 1; o < LANES; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
 __device__ __forceinline__ float softplus_f(float z) {  // log(1 + e^z), exact for any z
@@ -119,7 +120,7 @@ template <int N> __device__ __forceinline__ void copy_wait() {
 __device__ __forceinline__ void stage_tile(float* dst, const float* src, long long ld, int rows,
                                            int width, int vec) {
   const int per_row = width / vec;
-  for (int idx = threadIdx.x; idx < rows * per_row; idx += SCAN_THREADS) {
+  for (int idx = threadIdx.x; idx < rows * per_row; idx += blockDim.x) {
     const int i = idx / per_row, j = (idx % per_row) * vec;
     copy_async(dst + (size_t)i * width + j, src + (size_t)i * ld + j, vec);
   }
@@ -128,7 +129,7 @@ __device__ __forceinline__ void stage_tile(float* dst, const float* src, long lo
 __device__ __forceinline__ void stage_columns(float* dst, const float* src, long long ld,
                                               int rows, int p0, int P, int vec) {
   const int per_row = SCAN_COLS / vec;
-  for (int idx = threadIdx.x; idx < rows * per_row; idx += SCAN_THREADS) {
+  for (int idx = threadIdx.x; idx < rows * per_row; idx += blockDim.x) {
     const int i = idx / per_row, j = (idx % per_row) * vec;
     float* to = dst + i * SCAN_COLS + j;
     if (p0 + j < P) {  // (with vec 4, P is a multiple of 4: a group is inside or outside)
@@ -143,9 +144,9 @@ __device__ __forceinline__ void stage_columns(float* dst, const float* src, long
 // Mamba-2: per head h (group g = h / (heads / groups)), dt = softplus(dt_raw + dt_bias),
 //   S <- exp(-exp(A_log) dt) S + dt B x^T,   y = S^T C + D x,    S: [N x P].
 // xbc rows: [ x: heads x P | B: groups x N | C: groups x N ] (after convolution and silu).
-// State of a request's slot: S as [heads][N][P] from `state`.
-template <int RN>  // entries of a column per lane: N <= SCAN_LANES * RN
-__global__ void __launch_bounds__(SCAN_THREADS)
+// State of a request's slot: S as [heads][P][N] from `state`.
+template <int RN, int LANES>  // entries of a column per lane: N <= LANES * RN
+__global__ void __launch_bounds__(SCAN_COLS * LANES)
 mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __restrict__ dt_raw,
                    int ld_dt, const float* __restrict__ dt_bias,
                    const float* __restrict__ a_log, const float* __restrict__ skip,
@@ -157,7 +158,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __res
   const int stage_floats = chunk * (2 * N + SCAN_COLS + 4);
   pdl_launch_dependents();
   const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * SCAN_COLS;
-  const int col = threadIdx.x / SCAN_LANES, part = threadIdx.x % SCAN_LANES;
+  const int col = threadIdx.x / LANES, part = threadIdx.x % LANES;
   const int p = p0 + col;
   const bool live = p < P;
   const int g = h / (heads / groups), inner = heads * P;
@@ -168,39 +169,39 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __res
   float s[RN];
 #pragma unroll
   for (int k = 0; k < RN; ++k) {
-    const int n = part + SCAN_LANES * k;
-    s[k] = (live && n < N) ? mine[(size_t)n * P + p] : 0.f;
+    const int n = part + LANES * k;
+    s[k] = (live && n < N) ? mine[(size_t)p * N + n] : 0.f;
   }
   const int chunks = (rows + chunk - 1) / chunk;
   auto stage = [&](int c) {
-    float* at = scan_smem + (size_t)(c & 1) * stage_floats;
+    float* at = scan_smem + (size_t)(c % SCAN_STAGES) * stage_floats;
     const int t0 = c * chunk, count = min(chunk, rows - t0);
     const float* first = xbc + (size_t)(r0 + t0) * ld_xbc;
     stage_tile(at, first + inner + g * N, ld_xbc, count, N, vec);                          // B
     stage_tile(at + (size_t)chunk * N, first + inner + (groups + g) * N, ld_xbc, count, N, vec);
     stage_columns(at + (size_t)2 * chunk * N, first + h * P, ld_xbc, count, p0, P, vec);   // x
-    for (int i = threadIdx.x; i < count; i += SCAN_THREADS) {                              // dt
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {                              // dt
       copy_async(at + 2 * chunk * N + chunk * SCAN_COLS + i,
                  dt_raw + (size_t)(r0 + t0 + i) * ld_dt + h, 1);
     }
     copy_commit();
   };
-  stage(0);
+  for (int c = 0; c < SCAN_STAGES - 1; ++c) {
+    if (c < chunks) stage(c); else copy_commit();
+  }
   for (int c = 0; c < chunks; ++c) {
-    if (c + 1 < chunks) {
-      stage(c + 1);
-      copy_wait<1>();
-    } else {
-      copy_wait<0>();
-    }
+    // (one group per turn, staged or empty, so that the count of groups in flight says
+    // which chunk has landed)
+    if (c + SCAN_STAGES - 1 < chunks) stage(c + SCAN_STAGES - 1); else copy_commit();
+    copy_wait<SCAN_STAGES - 1>();
     __syncthreads();
-    float* b_s = scan_smem + (size_t)(c & 1) * stage_floats;
+    float* b_s = scan_smem + (size_t)(c % SCAN_STAGES) * stage_floats;
     float* c_s = b_s + (size_t)chunk * N;
     float* x_s = c_s + (size_t)chunk * N;
     float* dt_s = x_s + chunk * SCAN_COLS;   // raw, then the step size
     float* decay_s = dt_s + chunk;
     const int t0 = c * chunk, count = min(chunk, rows - t0);
-    for (int i = threadIdx.x; i < count; i += SCAN_THREADS) {
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
       const float dt = softplus_f(dt_s[i] + bias);
       dt_s[i] = dt;
       decay_s[i] = expf(rate * dt);
@@ -214,21 +215,21 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __res
       float acc = 0.f;
 #pragma unroll
       for (int k = 0; k < RN; ++k) {
-        const int n = part + SCAN_LANES * k;
+        const int n = part + LANES * k;
         if (n < N) {
           s[k] = fmaf(decay, s[k], push * bi[n]);
           acc = fmaf(s[k], ci[n], acc);
         }
       }
-      acc = group_sum8(acc);
+      acc = group_sum<LANES>(acc);
       if (part == 0 && live) y[(size_t)(r0 + t0 + i) * ld_y + h * P + p] = acc + d_skip * xv;
     }
-    __syncthreads();  // the buffer is staged again two chunks on
+    __syncthreads();  // the buffer is staged again at the next turn
   }
 #pragma unroll
   for (int k = 0; k < RN; ++k) {
-    const int n = part + SCAN_LANES * k;
-    if (live && n < N) mine[(size_t)n * P + p] = s[k];
+    const int n = part + LANES * k;
+    if (live && n < N) mine[(size_t)p * N + n] = s[k];
   }
 }
 
@@ -239,10 +240,10 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __res
 //   S <- keep S + take k v^T;  n <- keep n + take k;
 //   out = S^T q / (max(|n . q|, e^(-m')) + 1e-6),   q times dim^(-1/2).
 // proj rows: [ q: H x dim | k: H x dim | v: H x P | (gate, not read here) | i_raw: H | f_raw: H ]
-// at the given offsets. State of a slot: S [H][dim][P]; then, once per tile of SCAN_COLS
+// at the given offsets. State of a slot: S [H][P][dim]; then, once per tile of SCAN_COLS
 // columns so that no CTA reads what another writes, n [H][tiles][dim] and m [H][tiles].
-template <int RN>
-__global__ void __launch_bounds__(SCAN_THREADS)
+template <int RN, int LANES>
+__global__ void __launch_bounds__(SCAN_COLS * LANES)
 mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int v_offset,
                   int i_offset, int f_offset, const float* __restrict__ gate_bias, float cap,
                   float* __restrict__ state, long long state_stride,
@@ -255,7 +256,7 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
   pdl_launch_dependents();
   const int h = blockIdx.x, b = blockIdx.y, tile = blockIdx.z, tiles = gridDim.z;
   const int p0 = tile * SCAN_COLS;
-  const int col = threadIdx.x / SCAN_LANES, part = threadIdx.x % SCAN_LANES;
+  const int col = threadIdx.x / LANES, part = threadIdx.x % LANES;
   const int p = p0 + col;
   const bool live = p < P;
   const int r0 = row_start[b], rows = row_start[b + 1] - r0;
@@ -270,14 +271,14 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
   float s[RN], nrm[RN];
 #pragma unroll
   for (int k = 0; k < RN; ++k) {
-    const int n = part + SCAN_LANES * k;
-    s[k] = (live && n < dim) ? mine[(size_t)n * P + p] : 0.f;
+    const int n = part + LANES * k;
+    s[k] = (live && n < dim) ? mine[(size_t)p * dim + n] : 0.f;
     nrm[k] = n < dim ? norm_mine[n] : 0.f;
   }
   if (threadIdx.x == 0) m_run = *max_mine;
   const int chunks = (rows + chunk - 1) / chunk;
   auto stage = [&](int c) {
-    float* at = scan_smem + (size_t)(c & 1) * stage_floats;
+    float* at = scan_smem + (size_t)(c % SCAN_STAGES) * stage_floats;
     const int t0 = c * chunk, count = min(chunk, rows - t0);
     const float* first = proj + (size_t)(r0 + t0) * ld_proj;
     stage_tile(at, first + h * dim, ld_proj, count, dim, vec);                               // q
@@ -285,45 +286,58 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
     stage_columns(at + (size_t)2 * chunk * dim, first + v_offset + h * P, ld_proj, count, p0, P,
                   vec);                                                                     // v
     float* gates = at + 2 * chunk * dim + chunk * SCAN_COLS;
-    for (int i = threadIdx.x; i < 2 * count; i += SCAN_THREADS) {
+    for (int i = threadIdx.x; i < 2 * count; i += blockDim.x) {
       const int row = i >> 1;
       copy_async(gates + (i & 1) * chunk + row,
                  first + (size_t)row * ld_proj + ((i & 1) ? i_offset : f_offset) + h, 1);
     }
     copy_commit();
   };
-  stage(0);
+  for (int c = 0; c < SCAN_STAGES - 1; ++c) {
+    if (c < chunks) stage(c); else copy_commit();
+  }
   for (int c = 0; c < chunks; ++c) {
-    if (c + 1 < chunks) {
-      stage(c + 1);
-      copy_wait<1>();
-    } else {
-      copy_wait<0>();
-    }
+    // (one group per turn, staged or empty, so that the count of groups in flight says
+    // which chunk has landed)
+    if (c + SCAN_STAGES - 1 < chunks) stage(c + SCAN_STAGES - 1); else copy_commit();
+    copy_wait<SCAN_STAGES - 1>();
     __syncthreads();
-    float* q_s = scan_smem + (size_t)(c & 1) * stage_floats;
+    float* q_s = scan_smem + (size_t)(c % SCAN_STAGES) * stage_floats;
     float* k_s = q_s + (size_t)chunk * dim;
     float* v_s = k_s + (size_t)chunk * dim;
     float* keep_s = v_s + chunk * SCAN_COLS;  // raw forget gate, log gate f, then the factor
     float* take_s = keep_s + chunk;           // raw input gate, log gate i, then the factor
     float* floor_s = take_s + chunk;          // e^(-m')
     const int t0 = c * chunk, count = min(chunk, rows - t0);
-    for (int i = threadIdx.x; i < count; i += SCAN_THREADS) {
-      take_s[i] = cap * tanhf((take_s[i] + bias_i) / cap);
-      keep_s[i] = log_sigmoid_f(cap * tanhf((keep_s[i] + bias_f) / cap));
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {  // the scalar recurrence of the maximum, in row order
-      float m = m_run;
-      for (int i = 0; i < count; ++i) {
-        const float f = keep_s[i], ig = take_s[i];
-        const float m_new = fmaxf(f + m, ig);
-        keep_s[i] = expf(f + m - m_new);
+    if (threadIdx.x < 32) {
+      // The gates of the chunk's rows, one lane each, and the running maximum by a scan:
+      // row i maps m to max(f_i + m, i_i); two such maps compose to one of the same form,
+      // (a, b) then (a', b') = (a + a', max(a' + b, b')), so five steps of a warp scan give
+      // every row the map from the chunk's start to itself (chunk <= 32 rows).
+      const int i = threadIdx.x;
+      const bool row = i < count;
+      const float ig = row ? cap * tanhf((take_s[i] + bias_i) / cap) : 0.f;
+      const float f = row ? log_sigmoid_f(cap * tanhf((keep_s[i] + bias_f) / cap)) : 0.f;
+      float a = f, bmax = row ? ig : -INFINITY;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float a_up = __shfl_up_sync(0xffffffffu, a, o);
+        const float b_up = __shfl_up_sync(0xffffffffu, bmax, o);
+        if (i >= o) {
+          bmax = fmaxf(a + b_up, bmax);
+          a += a_up;
+        }
+      }
+      const float m_new = fmaxf(a + m_run, bmax);
+      float m_old = __shfl_up_sync(0xffffffffu, m_new, 1);
+      if (i == 0) m_old = m_run;
+      __syncwarp();
+      if (row) {
+        keep_s[i] = expf(f + m_old - m_new);
         take_s[i] = expf(ig - m_new);
         floor_s[i] = expf(-m_new);
-        m = m_new;
       }
-      m_run = m;
+      if (i == count - 1) m_run = m_new;
     }
     __syncthreads();
     for (int i = 0; i < count; ++i) {
@@ -334,7 +348,7 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
       float acc = 0.f, dot = 0.f;
 #pragma unroll
       for (int k = 0; k < RN; ++k) {
-        const int n = part + SCAN_LANES * k;
+        const int n = part + LANES * k;
         if (n < dim) {
           const float kk = ki[n], qq = qi[n];
           s[k] = fmaf(keep, s[k], tv * kk);
@@ -343,28 +357,32 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
           dot = fmaf(nrm[k], qq, dot);
         }
       }
-      acc = group_sum8(acc) * q_scale;
-      dot = group_sum8(dot) * q_scale;
+      acc = group_sum<LANES>(acc) * q_scale;
+      dot = group_sum<LANES>(dot) * q_scale;
       if (part == 0 && live) {
         out[(size_t)(r0 + t0 + i) * ld_out + h * P + p] =
             acc / (fmaxf(fabsf(dot), floor_s[i]) + 1e-6f);
       }
     }
-    __syncthreads();  // the buffer is staged again two chunks on
+    __syncthreads();  // the buffer is staged again at the next turn
   }
 #pragma unroll
   for (int k = 0; k < RN; ++k) {
-    const int n = part + SCAN_LANES * k;
-    if (live && n < dim) mine[(size_t)n * P + p] = s[k];
+    const int n = part + LANES * k;
+    if (live && n < dim) mine[(size_t)p * dim + n] = s[k];
     if (col == 0 && n < dim) norm_mine[n] = nrm[k];
   }
   if (threadIdx.x == 0) *max_mine = m_run;
 }
 
-// rows of a chunk: two buffers of chunk * (2 n + SCAN_COLS + 4) floats stay under 48 KB
+// rows of a chunk (at most 32: a warp scans a chunk's gates), and the ring's bytes: up to
+// 68 KB, which a kernel has to be allowed once (allow_smem)
 inline int scan_chunk(int n) { return n <= 64 ? 32 : (n <= 128 ? 16 : 8); }
 inline size_t scan_smem_bytes(int chunk, int n) {
-  return (size_t)2 * chunk * (2 * n + SCAN_COLS + 4) * sizeof(float);
+  return (size_t)SCAN_STAGES * chunk * (2 * n + SCAN_COLS + 4) * sizeof(float);
+}
+template <typename K> inline void allow_smem(K kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
 }
 // 16-byte copies when every staged address is a multiple of 16 bytes, else 4-byte ones
 inline int scan_vec(const float* base, long long ld, int n, int P,
@@ -422,21 +440,26 @@ AYK_API int ayk_mamba2_scan(const float* xbc, int ld_xbc, const float* dt_raw, i
       requests > 65535) {
     return AYK_BAD_ARGUMENT;
   }
-  if (N > SCAN_LANES * 32 || (P + SCAN_COLS - 1) / SCAN_COLS > 65535) return AYK_TOO_LARGE;
+  if (N > SCAN_MAX_N || (P + SCAN_COLS - 1) / SCAN_COLS > 65535) return AYK_TOO_LARGE;
   const int chunk = scan_chunk(N);
   const size_t smem = scan_smem_bytes(chunk, N);
   const int vec = scan_vec(xbc, ld_xbc, N, P, {(long long)heads * P});
   const dim3 grid(heads, requests, (P + SCAN_COLS - 1) / SCAN_COLS);
-#define AYK_MAMBA(RN)                                                                          \
-  return launch_kernel(mamba2_scan_kernel<RN>, grid, dim3(SCAN_THREADS), smem,                 \
-                       (cudaStream_t)stream, 1, xbc, ld_xbc, dt_raw, ld_dt, dt_bias, a_log,    \
-                       skip, state, state_stride, row_start, state_slot, y, ld_y, heads,       \
-                       groups, N, P, chunk, vec)
-  if (N <= SCAN_LANES * 2) AYK_MAMBA(2);
-  if (N <= SCAN_LANES * 4) AYK_MAMBA(4);
-  if (N <= SCAN_LANES * 8) AYK_MAMBA(8);
-  if (N <= SCAN_LANES * 16) AYK_MAMBA(16);
-  AYK_MAMBA(32);
+#define AYK_MAMBA(RN, LANES)                                                                   \
+  {                                                                                            \
+    static const bool allowed = (allow_smem(mamba2_scan_kernel<RN, LANES>), true);             \
+    (void)allowed;                                                                             \
+    return launch_kernel(mamba2_scan_kernel<RN, LANES>, grid, dim3(SCAN_COLS * LANES), smem,   \
+                         (cudaStream_t)stream, 1, xbc, ld_xbc, dt_raw, ld_dt, dt_bias, a_log,  \
+                         skip, state, state_stride, row_start, state_slot, y, ld_y, heads,     \
+                         groups, N, P, chunk, vec);                                            \
+  }
+  if (N <= 8) AYK_MAMBA(1, 8);
+  if (N <= 16) AYK_MAMBA(2, 8);
+  if (N <= 32) AYK_MAMBA(4, 8);
+  if (N <= 64) AYK_MAMBA(4, 16);
+  if (N <= 128) AYK_MAMBA(4, 32);
+  AYK_MAMBA(8, 32);
 #undef AYK_MAMBA
 }
 
@@ -454,20 +477,25 @@ AYK_API int ayk_mlstm_scan(const float* proj, int ld_proj, int k_offset, int v_o
       state_stride < (long long)heads * dim * P + (long long)heads * tiles * (dim + 1)) {
     return AYK_BAD_ARGUMENT;
   }
-  if (dim > SCAN_LANES * 32 || tiles > 65535) return AYK_TOO_LARGE;
+  if (dim > SCAN_MAX_N || tiles > 65535) return AYK_TOO_LARGE;
   const int chunk = scan_chunk(dim);
   const size_t smem = scan_smem_bytes(chunk, dim);
   const int vec = scan_vec(proj, ld_proj, dim, P, {k_offset, v_offset});
   const dim3 grid(heads, requests, tiles);
-#define AYK_MLSTM(RN)                                                                          \
-  return launch_kernel(mlstm_scan_kernel<RN>, grid, dim3(SCAN_THREADS), smem,                  \
-                       (cudaStream_t)stream, 1, proj, ld_proj, k_offset, v_offset, i_offset,   \
-                       f_offset, gate_bias, cap, state, state_stride, row_start, state_slot,   \
-                       out, ld_out, heads, dim, P, chunk, vec)
-  if (dim <= SCAN_LANES * 2) AYK_MLSTM(2);
-  if (dim <= SCAN_LANES * 4) AYK_MLSTM(4);
-  if (dim <= SCAN_LANES * 8) AYK_MLSTM(8);
-  if (dim <= SCAN_LANES * 16) AYK_MLSTM(16);
-  AYK_MLSTM(32);
+#define AYK_MLSTM(RN, LANES)                                                                   \
+  {                                                                                            \
+    static const bool allowed = (allow_smem(mlstm_scan_kernel<RN, LANES>), true);              \
+    (void)allowed;                                                                             \
+    return launch_kernel(mlstm_scan_kernel<RN, LANES>, grid, dim3(SCAN_COLS * LANES), smem,    \
+                         (cudaStream_t)stream, 1, proj, ld_proj, k_offset, v_offset, i_offset, \
+                         f_offset, gate_bias, cap, state, state_stride, row_start, state_slot, \
+                         out, ld_out, heads, dim, P, chunk, vec);                              \
+  }
+  if (dim <= 8) AYK_MLSTM(1, 8);
+  if (dim <= 16) AYK_MLSTM(2, 8);
+  if (dim <= 32) AYK_MLSTM(4, 8);
+  if (dim <= 64) AYK_MLSTM(4, 16);
+  if (dim <= 128) AYK_MLSTM(4, 32);
+  AYK_MLSTM(8, 32);
 #undef AYK_MLSTM
 }

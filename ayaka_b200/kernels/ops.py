@@ -29,6 +29,7 @@ __all__ = [
     "head_linear",
     "kv_store",
     "latent_attention",
+    "latent_decode",
     "latent_prepare",
     "launch_count",
     "leaving_out",
@@ -86,7 +87,8 @@ def leaving_out(*classes: str) -> Iterator[None]:
 
 _TIMED = ("embed_rows", "layer_norm", "linear", "linear_kv", "kv_store", "attention",
           "attention_prefill", "attention_decode", "argmax", "sample", "rms_norm", "rope",
-          "latent_prepare", "head_linear", "latent_attention", "causal_conv_silu", "mamba2_scan",
+          "latent_prepare", "head_linear", "latent_attention", "latent_decode",
+          "causal_conv_silu", "mamba2_scan",
           "mlstm_scan")
 
 
@@ -901,6 +903,59 @@ def latent_attention(qa: torch.Tensor, pages: torch.Tensor, block_table: torch.T
         c_int(out.stride(0)), c_int(n), c_int(num_heads), c_int(rank), c_int(key_dim - rank),
         c_int(page_size), c_float(scale), c_int(window), c_int(_TYPE[qa.dtype]), _stream())
     check(status, op)
+
+
+def latent_decode_splits(rows: int, num_heads: int, reach: int,
+                         device: torch.device | None = None) -> int:
+    """Shares a row's keys are cut into by :func:`latent_decode`: about two CTAs per SM over
+    all rows, at least two tiles of 32 keys a share, at most 32 shares."""
+    tiles = reach // 32 + 2
+    groups = -(-num_heads // 32)
+    return max(1, min(2 * sm_count(device) // max(1, rows * groups), tiles // 2, 32))
+
+
+def latent_decode(qa: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                  request_of_row: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+                  partial: torch.Tensor, *, num_heads: int, rank: int, scale: float,
+                  window: int, rows: int, splits: int) -> bool:
+    """:func:`latent_attention` for steps of single rows: one CTA per (row, share of its
+    keys) serves every head, so a latent row leaves memory once. A head's result lands in the
+    first ``rank`` of its ``out.shape[1] / num_heads`` columns. ``partial`` is float32 scratch
+    of at least ``rows * num_heads * splits * (rank + 2)`` elements. Returns False, having
+    run nothing, for sizes the kernel does not take."""
+    op = "latent_decode"
+    if _left_out and op in _left_out:
+        return True
+    _need(op, "qa", qa, ndim=2)
+    _need(op, "out", out, qa.dtype, 2)
+    _need(op, "pages", pages, qa.dtype, 4)
+    _need(op, "partial", partial, torch.float32)
+    _need(op, "block_table", block_table, torch.int32, 2)
+    _need(op, "request_of_row", request_of_row, torch.int32, 1)
+    _need(op, "positions", positions, torch.int32, 1)
+    if qa.dtype not in _TYPE or not pages.is_contiguous() or pages.shape[1] != 1 or \
+            not partial.is_contiguous():
+        raise BackendError(f"{op}: contiguous float32 or bfloat16 pages [page, 1, slot, row]")
+    _, _, page_size, key_dim = pages.shape
+    if qa.shape[1] != num_heads * key_dim or out.shape[1] % num_heads or \
+            out.shape[1] // num_heads < rank or rank > key_dim or rows > out.shape[0] or \
+            rows > qa.shape[0] or rows > request_of_row.shape[0] or \
+            rows > positions.shape[0] or \
+            partial.numel() < rows * num_heads * splits * (rank + 2):
+        raise BackendError(f"{op}: shapes do not fit")
+    global _launches
+    status = library("latent_attention").ayk_latent_decode(
+        _ptr(qa), c_int(qa.stride(0)), _ptr(pages), _ptr(block_table),
+        c_int(block_table.stride(0)), _ptr(request_of_row), _ptr(positions), _ptr(partial),
+        _ptr(out), c_int(out.stride(0)), c_int(out.shape[1] // num_heads), c_int(rows),
+        c_int(num_heads), c_int(rank), c_int(key_dim - rank), c_int(page_size), c_float(scale),
+        c_int(window), c_int(splits), c_int(_TYPE[qa.dtype]), _stream())
+    if status == -6:  # AYK_NOT_TAKEN
+        _launches -= 1
+        return False
+    _launches += 1  # the merge of the shares is a launch of its own
+    check(status, op)
+    return True
 
 
 # ---- layers with a running state ------------------------------------------------------------

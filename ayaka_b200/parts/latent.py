@@ -97,7 +97,20 @@ class LatentAttention(Mixer):
             q_plain=q_plain, qa=qa, heads=heads, dim=self.dim, rot=self.rot, rank=rank, rows=n)
         # the queries' unrotated parts, taken to latent space: qa[:, h, :rank] = W_uk,h^T q
         ops.head_linear(q_plain, self.up_key, qa, heads=heads, transposed=True, rows=n)
-        if shared:
+        taken = False
+        if step.decode_only:
+            # single rows: the kernel that fetches a latent row once for all heads
+            reach = min(step.max_kv_len, self.window) if self.window else step.max_kv_len
+            splits = ops.latent_decode_splits(n, heads, reach, hidden.device)
+            partial = work.buffer("latent.partial", heads * (rank + 2), torch.float32,
+                                  rows=n * splits)
+            taken = ops.latent_decode(qa, cache.k_pages, group.block_table,
+                                      step.request_of_row, step.positions, mixed, partial,
+                                      num_heads=heads, rank=rank, scale=self.scale,
+                                      window=self.window, rows=n, splits=splits)
+        if taken:
+            pass
+        elif shared:
             attend_paged(qa, cache.k_pages, cache.k_pages, mixed, step, group, num_heads=heads,
                          scale=self.scale, window=self.window, dtype=dtype)
         else:

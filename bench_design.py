@@ -167,7 +167,8 @@ def _measure(config: dict, peak: dict) -> dict:
                 # (attention over latent rows runs in the engine's own attention kernels
                 # where the row's size is one they take)
                 left = {"attention": ("attention_decode",),
-                        "latent_attention": ("latent_attention", "attention_decode")}.get(
+                        "latent_attention": ("latent_attention", "latent_decode",
+                                             "attention_decode")}.get(
                             name, (name,))
                 with ops.leaving_out(*left):
                     without = _timed_graph(body, 5)

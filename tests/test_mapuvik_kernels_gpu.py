@@ -171,6 +171,58 @@ def test_latent_attention_sees_its_window_and_not_a_key_more(dtype, heads, rank,
               f"request {b} position {p}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, rank, rot, window, page, splits", [
+    (3, 24, 8, 13, 8, 1), (5, 40, 0, 0, 16, 3), (16, 224, 32, 200, 16, 7), (37, 64, 16, 70, 32, 2),
+    (2, 250, 6, 0, 16, 32), (2, 20, 2, 0, 16, 2)])
+def test_latent_decode_serves_every_head_from_one_fetch(dtype, heads, rank, rot, window, page,
+                                                         splits):
+    """Single rows at the ends of sequences of every length around a tile of 32 keys and a
+    page, more shares than some rows have tiles, a window's oldest key loud and the key before
+    it louder; against the plain softmax, and against the kernel for any step."""
+    key_dim = rank + rot
+    lengths = [1, 2, 31, 32, 33, 64, 65, 300, page, page + 1]
+    keys = [randn(t, key_dim, seed=60 + i, scale=0.3) for i, t in enumerate(lengths)]
+    direction = randn(key_dim, seed=10)
+    direction = direction / direction.norm()
+    queries = []
+    for b, t in enumerate(lengths):
+        p = t - 1
+        oldest = max(0, p - window + 1) if window else 0
+        keys[b][oldest] += 6.0 * direction
+        if oldest > 0:
+            keys[b][oldest - 1] += 12.0 * direction
+        queries.append(randn(heads, key_dim, seed=200 + b, scale=0.5) + 3.0 * direction)
+    keys = [k.to(dtype).double() for k in keys]
+    q = torch.stack(queries).to(dtype)
+    pages, table = _paged(keys, page, dtype, shuffle_seed=4)
+    n, scale = len(lengths), 0.6
+    request_of_row = torch.arange(n, dtype=torch.int32, device=DEV)
+    positions = torch.tensor([t - 1 for t in lengths], dtype=torch.int32, device=DEV)
+    out = torch.full((n, heads * (rank + 5)), 7.0, dtype=dtype, device=DEV)  # padded heads
+    partial = torch.empty(n * heads * splits * (rank + 2), device=DEV)
+    took = ops.latent_decode(q.reshape(n, heads * key_dim).to(DEV), pages, table, request_of_row,
+                             positions, out, partial, num_heads=heads, rank=rank, scale=scale,
+                             window=window, rows=n, splits=splits)
+    if key_dim % 8:
+        assert not took
+        return
+    assert took
+    got = out.double().cpu().reshape(n, heads, rank + 5)
+    assert torch.all(got[..., rank:] == 7.0)
+    other = torch.zeros(n, heads * rank, dtype=dtype, device=DEV)
+    ops.latent_attention(q.reshape(n, heads * key_dim).to(DEV), pages, table, request_of_row,
+                         positions, other, num_heads=heads, rank=rank, scale=scale,
+                         window=window)
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    for b, t in enumerate(lengths):
+        lo = max(0, t - window) if window else 0
+        seen = keys[b][lo:t]
+        weights = torch.softmax(scale * q[b].double() @ seen.T, dim=-1)
+        close(got[b, :, :rank], weights @ seen[:, :rank], tol, f"request {b}")
+    close(got[..., :rank], other.double().cpu().reshape(n, heads, rank), tol, "both kernels")
+
+
 # ---- the short convolution --------------------------------------------------------------------
 @pytest.mark.parametrize("channels, taps", [(5, 1), (130, 2), (64, 4), (300, 7)])
 def test_the_convolution_carries_its_last_inputs_through_any_cut(channels, taps):
