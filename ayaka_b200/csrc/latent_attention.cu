@@ -347,9 +347,12 @@ latent_decode_kernel(const T* __restrict__ qa, int ld_qa, const T* __restrict__ 
     T* at = tile_s + (size_t)buffer * 32 * row_elems;
     for (int idx = threadIdx.x; idx < 32 * pieces; idx += LD_WARPS * 32) {
       const int j = idx / pieces, c = idx % pieces, t = tile * 32 + j;
+      T* to = at + (size_t)j * row_elems + c * PER16;
       if (t >= lo && t <= p) {
         const T* src = pages + ((size_t)table[t / page_size] * page_size + t % page_size) * key_dim;
-        la_copy16(at + (size_t)j * row_elems + c * PER16, src + c * PER16);
+        la_copy16(to, src + c * PER16);
+      } else {  // a key out of sight: zeros, so that its weight of 0 meets no stale NaN
+        *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -375,7 +378,6 @@ latent_decode_kernel(const T* __restrict__ qa, int ld_qa, const T* __restrict__ 
     const T* at = tile_s + (size_t)buffer * 32 * row_elems;
     const int t = tile * 32 + lane;
     const bool valid = t >= lo && t <= p;
-    const int count = min(32, p - tile * 32 + 1);
 #pragma unroll
     for (int u = 0; u < LD_HEADS; ++u) {
       const int h = warp + LD_WARPS * u;
@@ -384,14 +386,19 @@ latent_decode_kernel(const T* __restrict__ qa, int ld_qa, const T* __restrict__ 
       float score = -INFINITY;
       if (valid) {
         const T* key = at + (size_t)lane * row_elems;
-        float dot = 0.f;
+        float dot[4] = {0.f, 0.f, 0.f, 0.f};  // four chains: the sum is not one long wait
+#pragma unroll 4
         for (int d = 0; d < key_dim; d += 8) {
           float kv[8];
           Chunk8<T>::load(key + d, kv);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(q[d + e], kv[e], dot);
+          const float4 qa0 = *reinterpret_cast<const float4*>(q + d);
+          const float4 qa1 = *reinterpret_cast<const float4*>(q + d + 4);
+          dot[0] = fmaf(qa0.x, kv[0], dot[0]); dot[1] = fmaf(qa0.y, kv[1], dot[1]);
+          dot[2] = fmaf(qa0.z, kv[2], dot[2]); dot[3] = fmaf(qa0.w, kv[3], dot[3]);
+          dot[0] = fmaf(qa1.x, kv[4], dot[0]); dot[1] = fmaf(qa1.y, kv[5], dot[1]);
+          dot[2] = fmaf(qa1.z, kv[6], dot[2]); dot[3] = fmaf(qa1.w, kv[7], dot[3]);
         }
-        score = dot;
+        score = (dot[0] + dot[1]) + (dot[2] + dot[3]);
       }
       const float m_new = fmaxf(m[u], warp_max(score));
       const float wgt = valid ? expf(score - m_new) : 0.f;
@@ -404,9 +411,9 @@ latent_decode_kernel(const T* __restrict__ qa, int ld_qa, const T* __restrict__ 
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[u][e] *= corr;
       if (lane * 8 < rank) {
-        for (int j = 0; j < count; ++j) {
+#pragma unroll 8
+        for (int j = 0; j < 32; ++j) {  // (rows out of sight are zeros with weight 0)
           const float wj = w_s[warp][j];
-          if (wj == 0.f) continue;  // (also every key before the window)
           float vv[8];
           Chunk8<T>::load(at + (size_t)j * row_elems + lane * 8, vv);
 #pragma unroll
@@ -432,28 +439,38 @@ latent_decode_kernel(const T* __restrict__ qa, int ld_qa, const T* __restrict__ 
   }
 }
 
+constexpr int LD_MAX_SPLITS = 64;
+
 template <typename T>
 __global__ void latent_decode_merge_kernel(const float* __restrict__ partial,
                                            T* __restrict__ out, int ld_out, int out_head,
                                            int num_heads, int rank, int splits) {
+  __shared__ float max_s[LD_MAX_SPLITS], weight_s[LD_MAX_SPLITS];
   pdl_launch_dependents();
   const int row = blockIdx.x, head = blockIdx.y;
   pdl_wait_for(partial);
   const float* from = partial + ((size_t)row * num_heads + head) * splits * (rank + 2);
-  float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, from[(size_t)s * (rank + 2)]);
-  float l = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float* share = from + (size_t)s * (rank + 2);
-    if (share[1] > 0.f) l += share[1] * expf(share[0] - m);
+  for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+    max_s[s] = from[(size_t)s * (rank + 2)];
+    weight_s[s] = from[(size_t)s * (rank + 2) + 1];
   }
+  __syncthreads();
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, max_s[s]);
+  float l = 0.f;
+  for (int s = 0; s < splits; ++s) {  // (a share without keys has sum 0 and maximum -inf)
+    l += weight_s[s] > 0.f ? weight_s[s] * expf(max_s[s] - m) : 0.f;
+  }
+  __syncthreads();
+  for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+    weight_s[s] = weight_s[s] > 0.f ? expf(max_s[s] - m) : 0.f;
+  }
+  __syncthreads();
   T* dst = out + (size_t)row * ld_out + (size_t)head * out_head;
   for (int d = threadIdx.x; d < rank; d += blockDim.x) {
     float v = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float* share = from + (size_t)s * (rank + 2);
-      if (share[1] > 0.f) v += share[2 + d] * expf(share[0] - m);
-    }
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) v = fmaf(from[(size_t)s * (rank + 2) + 2 + d], weight_s[s], v);
     stf(dst + d, l > 0.f ? v / l : 0.f);
   }
 }
@@ -586,7 +603,7 @@ AYK_API int ayk_latent_decode(const void* qa, int ld_qa, const void* pages,
   if (rows == 0) return AYK_OK;
   const int key_dim = rank + rot;
   if (rows < 0 || num_heads < 1 || rank < 1 || rot < 0 || page_size < 1 || window < 0 ||
-      splits < 1 || splits > 65535 || qa == nullptr || pages == nullptr ||
+      splits < 1 || splits > LD_MAX_SPLITS || qa == nullptr || pages == nullptr ||
       block_table == nullptr || request_of_row == nullptr || positions == nullptr ||
       partial == nullptr || out == nullptr || ld_qa < num_heads * key_dim || out_head < rank ||
       (type != 0 && type != 1)) {

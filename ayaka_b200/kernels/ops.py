@@ -908,10 +908,13 @@ def latent_attention(qa: torch.Tensor, pages: torch.Tensor, block_table: torch.T
 def latent_decode_splits(rows: int, num_heads: int, reach: int,
                          device: torch.device | None = None) -> int:
     """Shares a row's keys are cut into by :func:`latent_decode`: about two CTAs per SM over
-    all rows, at least two tiles of 32 keys a share, at most 32 shares."""
+    all rows, at least two tiles of 32 keys a share, and no share left without tiles (a
+    share is ``ceil(tiles / shares)`` tiles, so the count is rounded to what that fills)."""
     tiles = reach // 32 + 2
     groups = -(-num_heads // 32)
-    return max(1, min(2 * sm_count(device) // max(1, rows * groups), tiles // 2, 32))
+    want = max(1, min(2 * sm_count(device) // max(1, rows * groups), 64))
+    per = max(2, -(-tiles // want))
+    return max(1, min(-(-tiles // per), 64))
 
 
 def latent_decode(qa: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,

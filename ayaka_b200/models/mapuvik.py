@@ -141,11 +141,12 @@ def _generator(seed: int, name: str) -> torch.Generator:
 
 def _random_tensors(config: MapuvikConfig, seed: int,
                     init: RandomInit) -> Iterator[tuple[str, torch.Tensor]]:
-    """Random float32 tensors under checkpoint names. Matrices are drawn with deviation
-    ``weight_std * sqrt(width / fan_in) ``... scaled so that a product keeps the size of its
-    input: ``std / sqrt(fan_in)`` with ``std = weight_std * sqrt(width)``; norm weights (stored
-    as deviations from one, or plain ones around one) with ``norm_std``; gate and step-size
-    parameters in the ranges in which the recurrences neither freeze nor forget at once."""
+    """Random float32 tensors under checkpoint names. A matrix is drawn with deviation
+    ``weight_std * sqrt(width / fan_in)``, so that a product keeps the size of its input
+    whatever its inner width; norm weights (stored as deviations from one, or plain ones around
+    one) with ``norm_std``; gate and step-size parameters in ranges in which the recurrences
+    neither freeze nor forget at once. Each tensor has its own generator, seeded from
+    ``seed`` and its name."""
     width = config.width
     loud = init.weight_std * math.sqrt(width)
 
