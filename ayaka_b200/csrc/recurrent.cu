@@ -8,7 +8,7 @@
 // [n x p] per head, so the p columns of S never mix: a CTA owns one (head, request, tile of
 // SCAN_COLS columns); a column's n entries are spread over LANES neighbouring lanes (8, 16 or
 // a whole warp, by the size of n: entry n on lane n % LANES, so that a thread holds at most
-// 8 entries and a device has thousands of warps to run), which add up their shares of y with
+// 16 entries and a device has thousands of warps to run), which add up their shares of y with
 // shuffles. A column is kept with its n entries side by side ([head][p][n]). The
 // rows are taken in chunks: the chunk's inputs are brought to shared memory by all threads
 // (and the gates turned into factors there, one thread per row), then every thread walks the
@@ -20,7 +20,7 @@
 namespace ayk {
 
 constexpr int SCAN_COLS = 16;   // columns of the state per CTA
-constexpr int SCAN_MAX_N = 256;  // entries of a column: 32 lanes x 8
+constexpr int SCAN_MAX_N = 512;  // entries of a column: 32 lanes x 16
 constexpr int CONV_MAX_TAPS = 16;
 constexpr int SCAN_STAGES = 4;  // buffers of staged chunks: three travel while one is walked
 
@@ -377,7 +377,7 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
 
 // rows of a chunk (at most 32: a warp scans a chunk's gates), and the ring's bytes: up to
 // 68 KB, which a kernel has to be allowed once (allow_smem)
-inline int scan_chunk(int n) { return n <= 64 ? 32 : (n <= 128 ? 16 : 8); }
+inline int scan_chunk(int n) { return n <= 64 ? 32 : (n <= 128 ? 16 : (n <= 256 ? 8 : 4)); }
 inline size_t scan_smem_bytes(int chunk, int n) {
   return (size_t)SCAN_STAGES * chunk * (2 * n + SCAN_COLS + 4) * sizeof(float);
 }
@@ -459,7 +459,8 @@ AYK_API int ayk_mamba2_scan(const float* xbc, int ld_xbc, const float* dt_raw, i
   if (N <= 32) AYK_MAMBA(4, 8);
   if (N <= 64) AYK_MAMBA(4, 16);
   if (N <= 128) AYK_MAMBA(4, 32);
-  AYK_MAMBA(8, 32);
+  if (N <= 256) AYK_MAMBA(8, 32);
+  AYK_MAMBA(16, 32);
 #undef AYK_MAMBA
 }
 
@@ -496,6 +497,7 @@ AYK_API int ayk_mlstm_scan(const float* proj, int ld_proj, int k_offset, int v_o
   if (dim <= 32) AYK_MLSTM(4, 8);
   if (dim <= 64) AYK_MLSTM(4, 16);
   if (dim <= 128) AYK_MLSTM(4, 32);
-  AYK_MLSTM(8, 32);
+  if (dim <= 256) AYK_MLSTM(8, 32);
+  AYK_MLSTM(16, 32);
 #undef AYK_MLSTM
 }

@@ -50,8 +50,8 @@ class Mamba2(Mixer):
         if self.norm_groups < 1 or self.inner % self.norm_groups:
             raise ValueError(f"norm_groups ({self.norm_groups}) must divide heads * columns "
                              f"({self.inner})")
-        if not 1 <= self.taps <= 16 or not 1 <= self.state <= 256:
-            raise ValueError("the convolution takes 1 to 16 taps, the state 1 to 256 entries")
+        if not 1 <= self.taps <= 16 or not 1 <= self.state <= 512:
+            raise ValueError("the convolution takes 1 to 16 taps, the state 1 to 512 entries")
         self.channels = self.inner + 2 * self.groups * self.state
         self.in_weight = self.add_param(
             "in.weight", (2 * self.inner + 2 * self.groups * self.state + self.num_heads,
@@ -119,8 +119,8 @@ class MLSTM(Mixer):
         self.columns = int(spec.columns)  # type: ignore[arg-type]
         self.gate_cap = float(spec.gate_cap)  # type: ignore[arg-type]
         self.eps = float(spec.eps)  # type: ignore[arg-type]
-        if not 1 <= self.dim <= 256 or self.columns < 1 or not self.gate_cap > 0:
-            raise ValueError("mlstm takes dim in [1, 256], columns >= 1 and a positive gate_cap")
+        if not 1 <= self.dim <= 512 or self.columns < 1 or not self.gate_cap > 0:
+            raise ValueError("mlstm takes dim in [1, 512], columns >= 1 and a positive gate_cap")
         heads = self.num_heads
         self.qk = heads * self.dim
         self.inner = heads * self.columns

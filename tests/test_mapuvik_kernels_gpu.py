@@ -276,7 +276,7 @@ def _cuts(total: int, sizes: tuple[int, ...]) -> list[tuple[int, int]]:
 
 
 @pytest.mark.parametrize("heads, groups, state_size, columns", [
-    (2, 1, 4, 5), (4, 2, 16, 16), (3, 3, 40, 24), (2, 2, 130, 33)])
+    (2, 1, 4, 5), (4, 2, 16, 16), (3, 3, 40, 24), (2, 2, 130, 33), (1, 1, 300, 9)])
 def test_the_state_space_recurrence_whole_and_in_portions(heads, groups, state_size, columns):
     total, inner = 70, heads * columns
     xbc = randn(total, inner + 2 * groups * state_size, seed=40, scale=0.7)
@@ -313,7 +313,7 @@ def test_the_state_space_recurrence_whole_and_in_portions(heads, groups, state_s
 
 
 @pytest.mark.parametrize("heads, dim, columns, cap", [(1, 4, 3, 5.0), (3, 16, 20, 15.0),
-                                                      (2, 72, 48, 8.0), (2, 200, 17, 30.0)])
+                                                      (2, 72, 48, 8.0), (2, 200, 17, 30.0), (1, 420, 7, 9.0)])
 def test_the_matrix_memory_whole_and_in_portions(heads, dim, columns, cap):
     total = 60
     qk, inner = heads * dim, heads * columns
