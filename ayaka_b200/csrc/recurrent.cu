@@ -87,6 +87,7 @@ __global__ void conv_state_update_kernel(const float* __restrict__ in, int ld_in
   const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
   if (c >= channels) return;
   const int r0 = row_start[b], rows = row_start[b + 1] - r0;
+  if (state_slot[b] < 0) return;  // a row of padding (a graph's bucket): no request, no state
   float* kept = state + (size_t)state_slot[b] * state_stride;
   pdl_wait_for(in, kept);
   float next[CONV_MAX_TAPS];
@@ -166,6 +167,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int ld_xbc, const float* __res
   const int g = h / (heads / groups), inner = heads * P;
   const int r0 = row_start[b], rows = row_start[b + 1] - r0;
   const float rate = -expf(a_log[h]), bias = dt_bias[h], d_skip = skip != nullptr ? skip[h] : 0.f;
+  if (state_slot[b] < 0) return;  // a row of padding (a graph's bucket): no request, no state
   float* mine = state + (size_t)state_slot[b] * state_stride + (size_t)h * N * P;
   pdl_wait_for(xbc, dt_raw, mine);
   float s[CP][RN];
@@ -284,6 +286,7 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
   const float q_scale = 1.f / sqrtf((float)dim);
   const float bias_i = gate_bias != nullptr ? gate_bias[h] : 0.f;
   const float bias_f = gate_bias != nullptr ? gate_bias[heads + h] : 0.f;
+  if (state_slot[b] < 0) return;  // a row of padding (a graph's bucket): no request, no state
   float* slot = state + (size_t)state_slot[b] * state_stride;
   float* mine = slot + (size_t)h * dim * P;
   float* norm_mine = slot + (size_t)heads * dim * P + ((size_t)h * tiles + tile) * dim;

@@ -160,9 +160,6 @@ class DecodeGraphs:
 
     def can_run(self, plan: object) -> bool:
         entries = plan.entries  # type: ignore[attr-defined]
-        if any(state is not None for state in self.core.cache_plan.run_state):
-            return False  # capture runs the step's kernels more than once: pages take that,
-            # a running per-request state does not
         return (plan.num_prefill_tokens == 0 and 0 < len(entries) <= self.sizes[-1]  # type: ignore
                 and len(plan.sampled) == len(entries))  # type: ignore[attr-defined]
 
@@ -259,13 +256,21 @@ class DecodeGraphs:
     def _capture(self, bucket: _Bucket, greedy: bool) -> None:
         core = self.core
         with torch.cuda.device(core.device):
-            # twice without capture: allocates the workspace, builds and configures kernels
+            # twice without capture: allocates the workspace, builds and configures kernels.
+            # Pages take a step that runs more than once (it stores the same again); running
+            # per-request states do not, so they are put back as they were before the capture
+            # (which records and does not run) and the replay that follows moves them once.
+            states = [state for state in core.storage.states if state is not None]
+            torch.cuda.synchronize(core.device)
+            saved = [state.clone() for state in states]
             side = torch.cuda.Stream(core.device)
             side.wait_stream(torch.cuda.current_stream(core.device))
             with torch.cuda.stream(side):
                 bucket.launch_body(core, greedy)
                 bucket.launch_body(core, greedy)
             torch.cuda.current_stream(core.device).wait_stream(side)
+            for state, before in zip(states, saved):
+                state.copy_(before)
             torch.cuda.synchronize(core.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
@@ -295,6 +300,7 @@ class DecodeGraphs:
         host[bucket.o_positions:bucket.o_positions + count] = positions
         host[bucket.o_request:bucket.o_request + count] = np.arange(count)
         host[bucket.o_kv_len:bucket.o_kv_len + count] = positions + 1
+        host[bucket.o_state:bucket.o_state + size] = -1  # rows of padding have no state
         host[bucket.o_state:bucket.o_state + count] = slots
         live = np.arange(count)
         for group, (o_slots, o_table) in enumerate(bucket.o_groups):

@@ -49,6 +49,8 @@ class LLM:
         self._pending: dict[str, deque[RequestEvent]] = {}
         self._requests: dict[str, object] = {}
         self._closed = False
+        plan = getattr(core, "cache_plan", None)
+        self._stateful = plan is not None and any(state is not None for state in plan.run_state)
         self.graphs = None
         if config.cuda_graph:
             from ayaka_b200.engine.graph import DecodeGraphs
@@ -191,7 +193,10 @@ class LLM:
             if graphs is not None and graphs.can_run(plan) and \
                     not any(row.adjusts for row in rows):
                 launch = graphs.launch(plan, rows)
-                following = self._rows_ahead(plan) if launch.exact else None
+                # (a launch made ahead may be dropped: pages take that, a running
+                # per-request state does not)
+                following = self._rows_ahead(plan) if launch.exact and not self._stateful \
+                    else None
                 if following is not None:
                     graphs.launch_ahead(launch, following)
                 picked = graphs.finish(launch)

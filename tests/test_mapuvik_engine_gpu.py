@@ -97,17 +97,24 @@ def test_greedy_generation_through_the_entry_point(tmp_path, graphs):
     prompts = [random_tokens(config["vocab"], n, 90 + n) for n in (1, 9, 40, 17, 3, 26)]
     wide = plain.cast_state(state, torch.float64)
     # a small budget and pool: prompts are cut into portions beside decoding requests, more
-    # requests than running slots, so state slots and pages are used again
-    engine = EngineConfig(model=str(folder), dtype="float32", max_running=3, num_blocks=20,
+    # requests than running slots, so state slots and pages are used again; requests end at
+    # different steps (their lengths differ), so the decode batch shrinks one by one
+    # (five running slots: graph buckets of 1, 2, 4 and 5 rows, so three live requests run
+    # in a bucket with a row of padding, which must leave every state alone)
+    engine = EngineConfig(model=str(folder), dtype="float32", max_running=5, num_blocks=20,
                           max_tokens_per_step=24, cuda_graph=graphs)
     with LLM.from_config(engine) as llm:
+        lengths = [12, 5, 9, 12, 3, 7]
         outputs = llm.generate([tuple(p) for p in prompts],
-                               SamplingParams(temperature=0.0, max_tokens=12))
+                               [SamplingParams(temperature=0.0, max_tokens=n) for n in lengths])
         llm.core.manager.check_integrity()
         assert not llm.core.manager.live_requests()
-    for prompt, output in zip(prompts, outputs):
+        if graphs:  # decode steps came from captured graphs, states carried through them
+            assert llm.graphs.replays > 0 and llm.graphs.adopted == 0
+    for prompt, output, length in zip(prompts, outputs, lengths):
         assert output.error is None
-        assert list(output.outputs[0].token_ids) == plain.greedy_generate(wide, config, prompt, 12)
+        assert list(output.outputs[0].token_ids) == \
+            plain.greedy_generate(wide, config, prompt, length)
 
 
 def test_the_replay_program_runs_a_mapuvik_folder(tmp_path):
