@@ -475,6 +475,235 @@ __global__ void latent_decode_merge_kernel(const float* __restrict__ partial,
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same for bfloat16 on the warp-level tensor cores: the (up to) 16 heads of a request are
+// the 16 rows of an mma.sync.m16n8k16 tile, so a tile of 32 latent rows is multiplied with all
+// heads in 64 instructions (scores) and 2 x rank / 8 more (weighted sum) instead of being read
+// once per head by the CUDA cores. A CTA of four warps takes one (row, share of keys, group
+// of 16 heads); each warp walks every fourth tile of the share on its own (its own two
+// buffers, filled by its own 16-byte asynchronous copies: no block barrier in the walk), keeps
+// the heads' running maxima and sums and the [16 x rank] accumulator in registers, and the four
+// warps' results are merged through shared memory into the share's (maximum, sum, weighted
+// rows), which latent_decode_merge_kernel joins with the other shares'. Weights are rounded to
+// bfloat16 as the A operand of the second product, like in the other tensor-core kernels.
+// Rows of rank + rot entries, a multiple of 16 up to 320; rank up to 256.
+constexpr int LM_WARPS = 4;
+inline int& decode_tensor_cores() {
+  static int enabled = 1;
+  return enabled;
+}
+
+__device__ __forceinline__ void lm_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void lm_ldmatrix_x4_trans(uint32_t* r, const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int NT16>  // the accumulator holds NT16 stretches of 16 entries: rank <= 16 * NT16
+__global__ void __launch_bounds__(LM_WARPS * 32)
+latent_decode_mma_kernel(const __nv_bfloat16* __restrict__ qa, int ld_qa,
+                         const __nv_bfloat16* __restrict__ pages,
+                         const int* __restrict__ block_table, int table_stride,
+                         const int* __restrict__ request_of_row,
+                         const int* __restrict__ positions, float* __restrict__ partial,
+                         int num_heads, int rank, int key_dim, int page_size, float scale,
+                         int window, int splits) {
+  extern __shared__ __align__(16) unsigned char lm_smem[];
+  const int stride = key_dim + 8;  // elements of a padded row (16 bytes more)
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);  // [16][stride]
+  __nv_bfloat16* tiles_s = q_s + 16 * stride;                      // [warps][2][32][stride]
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  const int row = blockIdx.x, split = blockIdx.y, head0 = blockIdx.z * 16;
+  const int heads_here = min(num_heads - head0, 16);
+  const int b = request_of_row[row], p = positions[row];
+  pdl_wait_for(qa, pages);
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int first_tile = lo / 32, tiles = b < 0 ? 0 : p / 32 - first_tile + 1;
+  const int per = (tiles + splits - 1) / splits;
+  const int t_begin = first_tile + split * per, t_end = min(first_tile + tiles, t_begin + per);
+  const int pieces = key_dim / 8;
+  for (int idx = threadIdx.x; idx < 16 * pieces; idx += LM_WARPS * 32) {
+    const int h = idx / pieces, c = idx % pieces;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);  // heads beyond the model's are rows of zeros
+    if (h < heads_here) {
+      v = *reinterpret_cast<const uint4*>(qa + (size_t)row * ld_qa +
+                                          (size_t)(head0 + h) * key_dim + c * 8);
+    }
+    *reinterpret_cast<uint4*>(q_s + (size_t)h * stride + c * 8) = v;
+  }
+  __syncthreads();
+  const int* table = block_table + (size_t)max(b, 0) * table_stride;
+  __nv_bfloat16* mine_s = tiles_s + (size_t)warp * 2 * 32 * stride;
+  auto stage = [&](int tile, int buffer) {
+    // key by key, the lanes side by side along the row: one request to memory brings 512
+    // consecutive bytes (lane j fetching row j would scatter every request over 32 rows)
+    // (lane j looks up where key j lies; the loop below asks it: a look-up inside the loop
+    // would wait behind the copies, which no load may pass)
+    const int t_mine = tile * 32 + lane;
+    long long where = -1;
+    if (t_mine >= lo && t_mine <= p) {
+      where = ((long long)table[t_mine / page_size] * page_size + t_mine % page_size) * key_dim;
+    }
+#pragma unroll 4
+    for (int j = 0; j < 32; ++j) {
+      __nv_bfloat16* to = mine_s + ((size_t)buffer * 32 + j) * stride;
+      const long long at = __shfl_sync(0xffffffffu, where, j);
+      if (at >= 0) {
+        const __nv_bfloat16* src = pages + at;
+        for (int c = lane; c < pieces; c += 32) la_copy16(to + c * 8, src + c * 8);
+      } else {
+        for (int c = lane; c < pieces; c += 32) {
+          *reinterpret_cast<uint4*>(to + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // heads g and g + 8
+  float o[2 * NT16][4];
+#pragma unroll
+  for (int n = 0; n < 2 * NT16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  int turn = 0;
+  if (t_begin + warp < t_end) stage(t_begin + warp, 0);
+  for (int tile = t_begin + warp; tile < t_end; tile += LM_WARPS, ++turn) {
+    const int buffer = turn & 1;
+    if (tile + LM_WARPS < t_end) {
+      stage(tile + LM_WARPS, buffer ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncwarp();
+    const __nv_bfloat16* at = mine_s + (size_t)buffer * 32 * stride;
+    // scores: [16 heads] x [32 keys], four stretches of 8 keys
+    float sc[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+    for (int k0 = 0; k0 < key_dim; k0 += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(q_s + (size_t)g * stride + k0 + 2 * t4);
+      a[1] = *reinterpret_cast<const uint32_t*>(q_s + (size_t)(g + 8) * stride + k0 + 2 * t4);
+      a[2] = *reinterpret_cast<const uint32_t*>(q_s + (size_t)g * stride + k0 + 8 + 2 * t4);
+      a[3] = *reinterpret_cast<const uint32_t*>(q_s + (size_t)(g + 8) * stride + k0 + 8 + 2 * t4);
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const __nv_bfloat16* key = at + (size_t)(n * 8 + g) * stride + k0 + 2 * t4;
+        lm_mma(sc[n], a, *reinterpret_cast<const uint32_t*>(key),
+               *reinterpret_cast<const uint32_t*>(key + 8));
+      }
+    }
+    // masks, running maxima and sums (a thread holds keys n * 8 + 2 t4 + {0, 1} of two heads)
+    float top[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int t = tile * 32 + n * 8 + 2 * t4 + (e & 1);
+        sc[n][e] = (t >= lo && t <= p) ? sc[n][e] * scale : -INFINITY;
+        top[e >> 1] = fmaxf(top[e >> 1], sc[n][e]);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 1));
+      top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 2));
+      const float m_new = fmaxf(m_run[r], top[r]);  // (every tile holds a key in sight)
+      corr[r] = expf(m_run[r] - m_new);
+      m_run[r] = m_new;
+      l_run[r] *= corr[r];
+    }
+    uint32_t pa[2][4];  // the weights as A operands: keys 0..15 and 16..31
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const float w0 = expf(sc[n][0] - m_run[0]), w1 = expf(sc[n][1] - m_run[0]);
+      const float w2 = expf(sc[n][2] - m_run[1]), w3 = expf(sc[n][3] - m_run[1]);
+      l_run[0] += w0 + w1;
+      l_run[1] += w2 + w3;
+      pa[n >> 1][(n & 1) * 2] = lm_pack(w0, w1);
+      pa[n >> 1][(n & 1) * 2 + 1] = lm_pack(w2, w3);
+    }
+#pragma unroll
+    for (int n = 0; n < 2 * NT16; ++n) {
+      o[n][0] *= corr[0];
+      o[n][1] *= corr[0];
+      o[n][2] *= corr[1];
+      o[n][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+      for (int c = 0; c < NT16; ++c) {
+        if (c * 16 < key_dim) {
+          uint32_t v[4];
+          lm_ldmatrix_x4_trans(v, at + (size_t)(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) *
+                                           stride + c * 16 + (lane >> 4) * 8);
+          lm_mma(o[2 * c], pa[kk], v[0], v[1]);
+          lm_mma(o[2 * c + 1], pa[kk], v[2], v[3]);
+        }
+      }
+    }
+    __syncwarp();  // the buffer is staged again at the next turn
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  // the four warps' results side by side in shared memory, then one (maximum, sum, rows)
+  __syncthreads();
+  const int width = 16 * NT16 + 2;
+  float* merge_s = reinterpret_cast<float*>(tiles_s);  // [warps][16][width]
+  {
+    float* mine = merge_s + (size_t)warp * 16 * width;
+    if (t4 == 0) {
+      mine[(size_t)g * width] = m_run[0];
+      mine[(size_t)g * width + 1] = l_run[0];
+      mine[(size_t)(g + 8) * width] = m_run[1];
+      mine[(size_t)(g + 8) * width + 1] = l_run[1];
+    }
+#pragma unroll
+    for (int n = 0; n < 2 * NT16; ++n) {
+      float* at = mine + 2 + n * 8 + 2 * t4;
+      at[(size_t)g * width] = o[n][0];
+      at[(size_t)g * width + 1] = o[n][1];
+      at[(size_t)(g + 8) * width] = o[n][2];
+      at[(size_t)(g + 8) * width + 1] = o[n][3];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < heads_here * (rank + 2); idx += LM_WARPS * 32) {
+    const int h = idx / (rank + 2), d = idx % (rank + 2);
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < LM_WARPS; ++w) m = fmaxf(m, merge_s[((size_t)w * 16 + h) * width]);
+    float value = 0.f;
+    if (d == 0) {
+      value = m;
+    } else {
+#pragma unroll
+      for (int w = 0; w < LM_WARPS; ++w) {
+        const float* from = merge_s + ((size_t)w * 16 + h) * width;
+        if (from[1] > 0.f) value += from[d] * expf(from[0] - m);  // d = 1: the sum
+      }
+    }
+    partial[(((size_t)row * num_heads + head0 + h) * splits + split) * (rank + 2) + d] = value;
+  }
+}
+
 template <typename T>
 int latent_attention(const void* qa, int ld_qa, const void* pages, const int* block_table,
                      int table_stride, const int* request_of_row, const int* positions, void* out,
@@ -502,6 +731,10 @@ int latent_attention(const void* qa, int ld_qa, const void* pages, const int* bl
 }  // namespace ayk
 
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
+
+// Whether single-row steps in bfloat16 may run on the warp-level tensor cores (the default) or
+// stay on the CUDA-core kernel (tests of that kernel, measurements of one against the other).
+AYK_API void ayk_set_latent_decode_tensor_cores(int on) { ayk::decode_tensor_cores() = on; }
 
 // type: 0 = float32, 1 = bfloat16 (cache, queries). pages may be null (a run that reads a
 // cache another run wrote) or a row's slot negative: nothing is stored then.
@@ -611,6 +844,36 @@ AYK_API int ayk_latent_decode(const void* qa, int ld_qa, const void* pages,
   }
   if (key_dim % 8 || key_dim > 320 || rank > 256 || ((uintptr_t)pages % 16)) return AYK_NOT_TAKEN;
   cudaStream_t s = (cudaStream_t)stream;
+  if (type == 1 && key_dim % 16 == 0 && ld_qa % 8 == 0 && ((uintptr_t)qa % 16) == 0 &&
+      decode_tensor_cores()) {
+    const int stretches = rank <= 64 ? 4 : (rank <= 128 ? 8 : (rank <= 192 ? 12 : 16));
+    const size_t walk = (size_t)LM_WARPS * 2 * 32 * (key_dim + 8) * 2;
+    const size_t merge = (size_t)LM_WARPS * 16 * (16 * stretches + 2) * sizeof(float);
+    const size_t bytes = (size_t)16 * (key_dim + 8) * 2 + (walk > merge ? walk : merge);
+    const dim3 mma_grid(rows, splits, (num_heads + 15) / 16);
+    int status = AYK_OK;
+#define AYK_LM(NT16)                                                                           \
+  {                                                                                            \
+    static const bool allowed =                                                                \
+        (cudaFuncSetAttribute(latent_decode_mma_kernel<NT16>,                                  \
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), true); \
+    (void)allowed;                                                                             \
+    status = launch_kernel(latent_decode_mma_kernel<NT16>, mma_grid, dim3(LM_WARPS * 32),      \
+                           bytes, s, 1, (const __nv_bfloat16*)qa, ld_qa,                       \
+                           (const __nv_bfloat16*)pages, block_table, table_stride,             \
+                           request_of_row, positions, partial, num_heads, rank, key_dim,       \
+                           page_size, scale, window, splits);                                  \
+  }
+    if (rank <= 64) AYK_LM(4)
+    else if (rank <= 128) AYK_LM(8)
+    else if (rank <= 192) AYK_LM(12)
+    else AYK_LM(16)
+#undef AYK_LM
+    if (status != AYK_OK) return status;
+    return launch_kernel(latent_decode_merge_kernel<__nv_bfloat16>, dim3(rows, num_heads),
+                         dim3(128), 0, s, 1, (const float*)partial, (__nv_bfloat16*)out, ld_out,
+                         out_head, num_heads, rank, splits);
+  }
   const int elem = type == 0 ? 4 : 2;
   const int group = LD_WARPS * LD_HEADS;
   const size_t smem = (size_t)2 * 32 * (key_dim + 16 / elem) * elem +

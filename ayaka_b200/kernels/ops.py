@@ -905,15 +905,23 @@ def latent_attention(qa: torch.Tensor, pages: torch.Tensor, block_table: torch.T
     check(status, op)
 
 
+def set_latent_decode_tensor_cores(enabled: bool) -> None:
+    """Let :func:`latent_decode` run bfloat16 steps on the warp-level tensor cores where the
+    sizes allow (the default), or keep every call on its CUDA-core kernel (tests of that
+    kernel, measurements of one against the other)."""
+    library("latent_attention").ayk_set_latent_decode_tensor_cores(c_int(1 if enabled else 0))
+
+
 def latent_decode_splits(rows: int, num_heads: int, reach: int,
                          device: torch.device | None = None) -> int:
-    """Shares a row's keys are cut into by :func:`latent_decode`: about two CTAs per SM over
-    all rows, at least two tiles of 32 keys a share, and no share left without tiles (a
-    share is ``ceil(tiles / shares)`` tiles, so the count is rounded to what that fills)."""
+    """Shares a row's keys are cut into by :func:`latent_decode`: about one CTA per SM over
+    all rows, at least four tiles of 32 keys a share (one for each warp of the tensor-core
+    kernel), and no share left without tiles (a share is ``ceil(tiles / shares)`` tiles, so
+    the count is rounded to what that fills)."""
     tiles = reach // 32 + 2
-    groups = -(-num_heads // 32)
-    want = max(1, min(2 * sm_count(device) // max(1, rows * groups), 64))
-    per = max(2, -(-tiles // want))
+    groups = -(-num_heads // 16)
+    want = max(1, min(sm_count(device) // max(1, rows * groups), 64))
+    per = max(4, -(-tiles // want))
     return max(1, min(-(-tiles // per), 64))
 
 

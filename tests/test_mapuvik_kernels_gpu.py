@@ -171,12 +171,13 @@ def test_latent_attention_sees_its_window_and_not_a_key_more(dtype, heads, rank,
               f"request {b} position {p}")
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype, tensor_cores", [(torch.float32, True), (torch.bfloat16, True),
+                                                 (torch.bfloat16, False)])
 @pytest.mark.parametrize("heads, rank, rot, window, page, splits", [
     (3, 24, 8, 13, 8, 1), (5, 40, 0, 0, 16, 3), (16, 224, 32, 200, 16, 7), (37, 64, 16, 70, 32, 2),
-    (2, 250, 6, 0, 16, 32), (2, 20, 2, 0, 16, 2)])
-def test_latent_decode_serves_every_head_from_one_fetch(dtype, heads, rank, rot, window, page,
-                                                         splits):
+    (2, 250, 6, 0, 16, 32), (2, 20, 2, 0, 16, 2), (20, 130, 30, 90, 16, 5), (1, 16, 0, 3, 8, 2)])
+def test_latent_decode_serves_every_head_from_one_fetch(dtype, tensor_cores, heads, rank, rot,
+                                                         window, page, splits):
     """Single rows at the ends of sequences of every length around a tile of 32 keys and a
     page, more shares than some rows have tiles, a window's oldest key loud and the key before
     it louder; against the plain softmax, and against the kernel for any step."""
@@ -201,9 +202,13 @@ def test_latent_decode_serves_every_head_from_one_fetch(dtype, heads, rank, rot,
     positions = torch.tensor([t - 1 for t in lengths], dtype=torch.int32, device=DEV)
     out = torch.full((n, heads * (rank + 5)), 7.0, dtype=dtype, device=DEV)  # padded heads
     partial = torch.empty(n * heads * splits * (rank + 2), device=DEV)
-    took = ops.latent_decode(q.reshape(n, heads * key_dim).to(DEV), pages, table, request_of_row,
-                             positions, out, partial, num_heads=heads, rank=rank, scale=scale,
-                             window=window, rows=n, splits=splits)
+    ops.set_latent_decode_tensor_cores(tensor_cores)
+    try:
+        took = ops.latent_decode(q.reshape(n, heads * key_dim).to(DEV), pages, table,
+                                 request_of_row, positions, out, partial, num_heads=heads,
+                                 rank=rank, scale=scale, window=window, rows=n, splits=splits)
+    finally:
+        ops.set_latent_decode_tensor_cores(True)
     if key_dim % 8:
         assert not took
         return
