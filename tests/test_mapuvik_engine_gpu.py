@@ -126,3 +126,34 @@ def test_the_replay_program_runs_a_mapuvik_folder(tmp_path):
                                     config["vocab"])
     support.assert_logits_close(got, plain_logits(state, config, sequences), "float32",
                                 "mapuvik-b/trace_run")
+
+
+def test_the_command_line_writes_and_runs_a_mapuvik_folder(tmp_path):
+    """``random`` writes a folder from a configuration file, ``run`` generates from it with the
+    engine's own sizing of the cache (the design has no longest sequence of its own)."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from ayaka_b200.weights.random_init import random_state
+    from ayaka_b200.weights.rules import RandomInit
+
+    root = Path(__file__).resolve().parent.parent
+    config_file = tmp_path / "config.json"
+    config_file.write_text(json.dumps(TINY_B))
+    folder = tmp_path / "model"
+    made = subprocess.run([sys.executable, "-m", "ayaka_b200", "random", str(config_file),
+                           str(folder), "--seed", "4", "--weight-std", "0.12", "--norm-std",
+                           "0.1"], capture_output=True, text=True, cwd=root, timeout=600)
+    assert made.returncode == 0, made.stderr
+    state = random_state(TINY_B, 4, RandomInit(weight_std=0.12, bias_std=0.0, norm_std=0.1))
+    prompt = random_tokens(TINY_B["vocab"], 21, 11)
+    done = subprocess.run(
+        [sys.executable, "-m", "ayaka_b200", "run", str(folder), "-p",
+         " ".join(map(str, prompt)), "--max-tokens", "9", "--dtype", "fp32"],
+        capture_output=True, text=True, cwd=root, timeout=600)
+    assert done.returncode == 0, done.stderr
+    wide = plain.cast_state(state, torch.float64)
+    assert [int(t) for t in done.stdout.split()] == plain.greedy_generate(wide, TINY_B, prompt, 9)
+    assert "5 layers" in done.stderr and "cache pages" in done.stderr
