@@ -1,4 +1,5 @@
-"""ayaka_b200: a single-GPU GPT-2 inference engine written for NVIDIA B200 (sm_100a).
+"""ayaka_b200: a single-GPU decoder inference engine (GPT-2, Mapuvik) written for NVIDIA B200
+(sm_100a).
 
 Public names are imported lazily so that ``import ayaka_b200`` never needs a GPU.
 """
@@ -11,6 +12,7 @@ _LAZY = {
     "LLM": "ayaka_b200.engine.llm",
     "EngineConfig": "ayaka_b200.config.engine",
     "GPT2Config": "ayaka_b200.config.model",
+    "MapuvikConfig": "ayaka_b200.config.mapuvik",
     "SamplingParams": "ayaka_b200.sampling.params",
     "RequestOutput": "ayaka_b200.engine.outputs",
 }

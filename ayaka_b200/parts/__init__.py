@@ -1,8 +1,9 @@
 """The parts a model is put together from, each registered under a kind name.
 
-Importing this package registers the built-in kinds: mixer ``attention``; feed-forward
-``dense``; norm ``layer_norm``; positions ``learned`` and ``none``; block ``pre_norm``;
-embedding ``token``; head ``linear``.
+Importing this package registers the built-in kinds: mixers ``attention``,
+``latent_attention``, ``mamba2`` and ``mlstm``; feed-forwards ``dense`` and ``none``; norms
+``layer_norm`` and ``rms_norm``; positions ``learned``, ``rotary`` and ``none``; blocks
+``pre_norm`` and ``parallel``; embedding ``token``; head ``linear``.
 """
 
 from ayaka_b200.parts import (block, embedding, feed_forward, latent, mixer, norm,  # noqa: F401

@@ -9,7 +9,8 @@ class's own kernels between CUDA events (``ops.timed``), in the decode step the 
 without the class (``ops.leaving_out``). A class's ``frac`` is its arithmetic over the measured
 bf16 peak (products and attention of the prompt step) or its bytes over the measured copy
 bandwidth (everything else), so that like kernels of the two models can be set side by side.
-One JSON line.
+``generate`` is the decode step through ``LLM.generate`` (scheduler, sampling and host time
+included, CUDA graphs on). One JSON line.
 """
 
 from __future__ import annotations
