@@ -157,3 +157,23 @@ def test_the_command_line_writes_and_runs_a_mapuvik_folder(tmp_path):
     wide = plain.cast_state(state, torch.float64)
     assert [int(t) for t in done.stdout.split()] == plain.greedy_generate(wide, TINY_B, prompt, 9)
     assert "5 layers" in done.stderr and "cache pages" in done.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_latent_rows_of_64_entries_in_long_portions(tmp_path, dtype):
+    """Key rows of 48 + 16 entries are a head size of 64: in bfloat16, portions of 256 rows and
+    more run on the tcgen05 attention kernel with the latent pages as keys and as values; a
+    window of 300 inside a prompt of 700, then decoding past it."""
+    from mapuvik_cases import latent, layer, model
+
+    config = model(150, 128, 1e-5, [layer(latent(4, 32, 16, 24, 48, 300), 64),
+                                    layer(latent(2, 16, 16, 40, 48, 1000, turned=8))])
+    folder, state = support.make_model(tmp_path / "m", config, 3, LOUD_WIDE, dtype)
+    sequences = _sequences(config, (700, 290), seed=6)
+    expected = plain_logits(state, config, sequences)
+    core = support.build_core(folder, dtype, num_blocks=70, max_running=2,
+                              max_tokens_per_step=1024)
+    got = support.replay(core, support.schedule_tail(sequences, tail=30))
+    support.assert_logits_close(got, expected, dtype, "mapuvik-64/tail")
+    got = support.replay(core, support.schedule_portions(sequences, sizes=(300, 2, 256, 1, 141)))
+    support.assert_logits_close(got, expected, dtype, "mapuvik-64/portions")
