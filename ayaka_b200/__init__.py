@@ -1,4 +1,4 @@
-"""ayaka_b200: a single-GPU decoder inference engine (GPT-2, Mapuvik) written for NVIDIA B200
+"""ayaka_b200: a single-GPU decoder inference engine (GPT-2, Mapuvik, Gagotar) written for NVIDIA B200
 (sm_100a).
 
 Public names are imported lazily so that ``import ayaka_b200`` never needs a GPU.
@@ -13,6 +13,7 @@ _LAZY = {
     "EngineConfig": "ayaka_b200.config.engine",
     "GPT2Config": "ayaka_b200.config.model",
     "MapuvikConfig": "ayaka_b200.config.mapuvik",
+    "GagotarConfig": "ayaka_b200.config.gagotar",
     "SamplingParams": "ayaka_b200.sampling.params",
     "RequestOutput": "ayaka_b200.engine.outputs",
 }

@@ -13,7 +13,9 @@ The three calls follow the reference's manager (``python/ayaka/kvcache/manager.p
 in all groups or in none, and returns ``False`` instead of raising or evicting when pages,
 a row or the table's width run out; ``commit(id, n)`` records that the step wrote them;
 ``free(id)`` gives everything back. Added here: a windowed group gives a page back as soon
-as a commit has moved the window past it, and freed pages are reused first (LIFO).
+as a commit has moved the window past it (a group whose rows see only their own block of
+positions, as soon as a commit has entered the next block), and freed pages are reused first
+(LIFO).
 """
 
 from __future__ import annotations
@@ -117,7 +119,7 @@ class CacheManager:
         below its window plus a page)."""
         limit = self.max_tokens_per_request
         for need, pool in zip(self.needs, self.pools):
-            if need.window == 0:
+            if not need.forgets:
                 limit = min(limit, pool.num_usable * self.page_size)
         return limit
 
@@ -128,11 +130,14 @@ class CacheManager:
         return max(0, -(-total // self.page_size) - first)
 
     def _first_live_page(self, group: int, committed: int) -> int:
-        window = self.needs[group].window
-        if window == 0:
+        need = self.needs[group]
+        if not need.forgets:
             return 0
-        # the next row sits at position `committed` and sees keys committed - window + 1 ..
-        oldest = max(0, committed - window + 1)
+        # the next row sits at position `committed`: it sees keys committed - window + 1 ..
+        # and, with blocks, nothing before the start of its own block of `chunk` positions
+        oldest = max(0, committed - need.window + 1) if need.window else 0
+        if need.chunk:
+            oldest = max(oldest, committed - committed % need.chunk)
         return oldest // self.page_size
 
     # ---- queries ------------------------------------------------------------------------
@@ -217,7 +222,7 @@ class CacheManager:
         held.committed += num_tokens
         held.reserved -= num_tokens
         for group, need in enumerate(self.needs):
-            if need.window == 0:
+            if not need.forgets:
                 continue
             table = self.tables[group][held.row]
             for index in range(self._first_live_page(group, before),

@@ -43,8 +43,8 @@ class CachePlan:
 
     def bytes_per_page(self, group: int, itemsize: int, page_size: int) -> int:
         need = self.groups[group]
-        return ((2 if need.values else 1) * self.slots_per_group[group] * need.num_kv_heads
-                * page_size * need.head_dim * itemsize)
+        entries = need.head_dim + (need.value_head_dim if need.values else 0)
+        return self.slots_per_group[group] * need.num_kv_heads * page_size * entries * itemsize
 
     def bytes_per_token(self, itemsize: int) -> int:
         """Key and value bytes one cached token takes over all groups (windows ignored)."""
@@ -99,8 +99,8 @@ class CacheStorage:
             shape = (slots, pages, need.num_kv_heads, page_size, need.head_dim)
             self.keys.append(torch.zeros(shape, dtype=dtype, device=device))
             # a group of latent rows keeps one tensor: its rows are keys and values at once
-            self.values.append(torch.zeros(shape, dtype=dtype, device=device)
-                               if need.values else None)
+            self.values.append(torch.zeros((*shape[:-1], need.value_head_dim), dtype=dtype,
+                                           device=device) if need.values else None)
         if poison:
             self.poison()
         self.states: list[torch.Tensor | None] = [

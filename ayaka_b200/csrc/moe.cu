@@ -1,0 +1,393 @@
+// Mixture of experts: routing, the experts' products over rows grouped by expert, the join.
+//
+// A step's rows each choose `top` of E experts. A (row, choice) is a *pair*; pair p = row *
+// top + choice. Four launches, none of which needs the host to know a count:
+//   route:   per row, the `top` largest router logits (fp32; ties to the smaller index) and
+//            the softmax over just those -> chosen[p], share[p];
+//   align:   pairs grouped by expert into a list whose every expert's stretch is padded to
+//            a multiple of the tile's rows (-1 = no pair), and the expert of every tile;
+//   experts: two grouped products over those tiles. The first computes, per pair,
+//            g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit) and writes
+//            y = g sigmoid(alpha g) (u + 1); the second writes W_down y per pair in fp32;
+//   join:    dst[row] (+)= scale * sum_choice share * (W_down y)[pair], choices in order.
+// A pair's result does not depend on its place in a tile or on the other pairs: every output
+// element is one sum over k in a fixed order. Experts' matrices lie one under the other:
+// w_in [E][2 * ff][width] (an expert's gate rows, then its up rows), w_out [E][width][ff].
+//
+// The tile products run on the CUDA cores with fp32 FMA for float32 and on the warp-level
+// tensor cores (mma.sync m16n8k16, fp32 accumulators) for bfloat16.
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace ayk {
+
+constexpr int MOE_TM = 32;   // pairs per tile
+constexpr int MOE_TN = 64;   // output columns per tile
+constexpr int MOE_TK = 32;   // k per turn
+constexpr int MOE_MAX_EXPERTS = 1024;
+
+// ---------------------------------------------------------------------------------------------
+// One warp per row. Lane l holds logits l, l + 32, ...; `top` times the largest not yet taken.
+__global__ void moe_route_kernel(const float* __restrict__ logits, int ld, int rows, int E,
+                                 int top, int* __restrict__ chosen, float* __restrict__ share) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  pdl_wait_for(logits);
+  const float* z = logits + (size_t)row * ld;
+  uint32_t taken = 0;  // bit m: entry lane + 32 m is chosen
+  float first = 0.f, total = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = INT_MAX;
+    for (int m = 0; lane + 32 * m < E; ++m) {
+      if (taken >> m & 1u) continue;
+      const float v = z[lane + 32 * m];
+      if (v > best || at == INT_MAX) {
+        best = v;
+        at = lane + 32 * m;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_at = __shfl_xor_sync(0xffffffffu, at, o);
+      if (other_at != INT_MAX && (at == INT_MAX || other > best ||
+                                  (other == best && other_at < at))) {
+        best = other;
+        at = other_at;
+      }
+    }
+    if ((at & 31) == lane) taken |= 1u << (at >> 5);
+    if (j == 0) first = best;
+    const float e = expf(best - first);  // the first is the largest: no overflow
+    total += e;
+    if (lane == 0) {
+      chosen[(size_t)row * top + j] = at;
+      share[(size_t)row * top + j] = e;
+    }
+  }
+  __syncwarp();
+  if (lane < top) share[(size_t)row * top + lane] /= total;
+  for (int j = 32 + lane; j < top; j += 32) share[(size_t)row * top + j] /= total;
+}
+
+// One CTA. sorted: [max_tiles * MOE_TM] pair indices or -1; tile_expert: [max_tiles], -1 for a
+// tile past the last.
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* __restrict__ chosen, int pairs, int E, int max_tiles,
+                 int* __restrict__ sorted, int* __restrict__ tile_expert) {
+  __shared__ int counts[MOE_MAX_EXPERTS];
+  __shared__ int starts[MOE_MAX_EXPERTS];
+  pdl_launch_dependents();
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E; e += blockDim.x) counts[e] = 0;
+  pdl_wait_for(chosen);
+  __syncthreads();
+  for (int p = tid; p < pairs; p += blockDim.x) {
+    const int e = chosen[p];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  for (int i = tid; i < max_tiles * MOE_TM; i += blockDim.x) sorted[i] = -1;
+  __syncthreads();
+  if (tid == 0) {
+    int tile = 0;
+    for (int e = 0; e < E; ++e) {
+      starts[e] = tile * MOE_TM;
+      const int tiles = (counts[e] + MOE_TM - 1) / MOE_TM;
+      for (int t = 0; t < tiles && tile < max_tiles; ++t) tile_expert[tile++] = e;
+      counts[e] = 0;  // now the cursor of the expert's stretch
+    }
+    for (; tile < max_tiles; ++tile) tile_expert[tile] = -1;
+  }
+  __syncthreads();
+  for (int p = tid; p < pairs; p += blockDim.x) {
+    const int e = chosen[p];
+    if (e >= 0 && e < E) sorted[starts[e] + atomicAdd(&counts[e], 1)] = p;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// A tile's product. PHASE 0: rows of `a` are the pairs' rows of the normed input (row = pair /
+// top), the weight tile is rows n0.. of the expert's gate part and of its up part, the result
+// y[place][n] in the compute type. PHASE 1: rows of `a` are y[place], the weight tile rows
+// n0.. of the expert's down matrix, the result out[pair][n] in fp32.
+__device__ __forceinline__ float expert_unit(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
+
+template <typename T, int PHASE> struct TileAcc;
+
+// fp32: thread (ty, tx) of 16 x 16 owns rows 2 ty .. +1 and columns 4 tx .. +3
+template <int PHASE> struct TileAcc<float, PHASE> {
+  static constexpr int LDS = MOE_TK + 1;
+  float acc[PHASE == 0 ? 2 : 1][2][4];
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int w = 0; w < (PHASE == 0 ? 2 : 1); ++w)
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[w][i][j] = 0.f;
+  }
+  __device__ __forceinline__ void step(const float* As, const float* Bs, const float* Bs2) {
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+#pragma unroll
+    for (int k = 0; k < MOE_TK; ++k) {
+      float av[2], bv[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) av[i] = As[(ty * 2 + i) * LDS + k];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bv[j] = Bs[(tx * 4 + j) * LDS + k];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[0][i][j] = fmaf(av[i], bv[j], acc[0][i][j]);
+      if (PHASE == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bv[j] = Bs2[(tx * 4 + j) * LDS + k];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[PHASE == 0 ? 1 : 0][i][j] =
+              fmaf(av[i], bv[j], acc[PHASE == 0 ? 1 : 0][i][j]);
+      }
+    }
+  }
+  template <typename F> __device__ __forceinline__ void each(F f) {
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        f(ty * 2 + i, tx * 4 + j, acc[0][i][j], acc[PHASE == 0 ? 1 : 0][i][j]);
+      }
+  }
+};
+
+// bfloat16: eight warps as 2 (rows of 16) x 4 (columns of 16); a warp holds two m16n8
+// accumulators per matrix. Shared rows are padded by 8 entries so that a fragment's eight
+// rows fall into different banks.
+template <int PHASE> struct TileAcc<__nv_bfloat16, PHASE> {
+  static constexpr int LDS = MOE_TK + 8;
+  float acc[PHASE == 0 ? 2 : 1][2][4];
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int w = 0; w < (PHASE == 0 ? 2 : 1); ++w)
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[w][i][j] = 0.f;
+  }
+  static __device__ __forceinline__ uint32_t pair_at(const __nv_bfloat16* p) {
+    return *reinterpret_cast<const uint32_t*>(p);
+  }
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4],
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  __device__ __forceinline__ void step(const __nv_bfloat16* As, const __nv_bfloat16* Bs,
+                                       const __nv_bfloat16* Bs2) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 16;
+#pragma unroll
+    for (int k0 = 0; k0 < MOE_TK; k0 += 16) {
+      uint32_t a[4];
+      a[0] = pair_at(As + (m0 + g) * LDS + k0 + 2 * t);
+      a[1] = pair_at(As + (m0 + g + 8) * LDS + k0 + 2 * t);
+      a[2] = pair_at(As + (m0 + g) * LDS + k0 + 2 * t + 8);
+      a[3] = pair_at(As + (m0 + g + 8) * LDS + k0 + 2 * t + 8);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const __nv_bfloat16* b = Bs + (n0 + 8 * j + g) * LDS + k0 + 2 * t;
+        mma(acc[0][j], a, pair_at(b), pair_at(b + 8));
+        if (PHASE == 0) {
+          const __nv_bfloat16* b2 = Bs2 + (n0 + 8 * j + g) * LDS + k0 + 2 * t;
+          mma(acc[PHASE == 0 ? 1 : 0][j], a, pair_at(b2), pair_at(b2 + 8));
+        }
+      }
+    }
+  }
+  template <typename F> __device__ __forceinline__ void each(F f) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 16;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        f(m0 + g + (i >> 1) * 8, n0 + 8 * j + 2 * t + (i & 1), acc[0][j][i],
+          acc[PHASE == 0 ? 1 : 0][j][i]);
+      }
+  }
+};
+
+template <typename T, int PHASE>
+__global__ void __launch_bounds__(256)
+moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
+                const int* __restrict__ sorted, const int* __restrict__ tile_expert, int top,
+                int K, int N, float limit, float alpha, T* __restrict__ y, int ld_y,
+                float* __restrict__ out, int ld_out) {
+  using Acc = TileAcc<T, PHASE>;
+  constexpr int LDS = Acc::LDS;
+  __shared__ __align__(16) T As[MOE_TM * LDS];
+  __shared__ __align__(16) T Bs[MOE_TN * LDS];
+  __shared__ __align__(16) T Bs2[PHASE == 0 ? MOE_TN * LDS : 1];
+  __shared__ int pair_s[MOE_TM];
+  pdl_launch_dependents();
+  const int tile = blockIdx.x, n0 = blockIdx.y * MOE_TN, tid = threadIdx.x;
+  pdl_wait_for(a, sorted, tile_expert);
+  const int e = tile_expert[tile];
+  if (e < 0) return;
+  if (tid < MOE_TM) pair_s[tid] = sorted[tile * MOE_TM + tid];
+  __syncthreads();
+  // an expert's matrices: PHASE 0 [2 N][K] (gate rows, then up rows), PHASE 1 [N][K]
+  const T* w = weight + (size_t)e * (PHASE == 0 ? 2 : 1) * N * K;
+  Acc acc;
+  acc.zero();
+  for (int k0 = 0; k0 < K; k0 += MOE_TK) {
+    for (int idx = tid; idx < MOE_TM * MOE_TK; idx += 256) {
+      const int r = idx / MOE_TK, k = idx % MOE_TK;
+      const int pair = pair_s[r];
+      T v = T(0.f);
+      if (pair >= 0 && k0 + k < K) {
+        const size_t row = PHASE == 0 ? (size_t)(pair / top) : (size_t)tile * MOE_TM + r;
+        v = a[row * lda + k0 + k];
+      }
+      As[r * LDS + k] = v;
+    }
+    for (int idx = tid; idx < MOE_TN * MOE_TK; idx += 256) {
+      const int r = idx / MOE_TK, k = idx % MOE_TK;
+      const bool in = n0 + r < N && k0 + k < K;
+      Bs[r * LDS + k] = in ? w[(size_t)(n0 + r) * K + k0 + k] : T(0.f);
+      if (PHASE == 0) Bs2[r * LDS + k] = in ? w[(size_t)(N + n0 + r) * K + k0 + k] : T(0.f);
+    }
+    __syncthreads();
+    acc.step(As, Bs, Bs2);
+    __syncthreads();
+  }
+  acc.each([&](int r, int c, float first, float second) {
+    const int pair = pair_s[r];
+    if (pair < 0 || n0 + c >= N) return;
+    if (PHASE == 0) {
+      stf(y + ((size_t)tile * MOE_TM + r) * ld_y + n0 + c,
+          expert_unit(first, second, limit, alpha));
+    } else {
+      out[(size_t)pair * ld_out + n0 + c] = first;
+    }
+  });
+}
+
+// dst[row][c] (+)= scale[c] * sum_j share[row * top + j] * pair_out[row * top + j][c]
+__global__ void moe_join_kernel(const float* __restrict__ pair_out, int ld, const float* __restrict__ share,
+                                int top, const float* __restrict__ scale,
+                                float* __restrict__ dst, int ld_dst, int width, int accumulate) {
+  pdl_launch_dependents();
+  const int row = blockIdx.x;
+  pdl_wait_for(pair_out, share, dst);
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const size_t pair = (size_t)row * top + j;
+      sum = fmaf(share[pair], pair_out[pair * ld + c], sum);
+    }
+    if (scale != nullptr) sum *= scale[c];
+    float* to = dst + (size_t)row * ld_dst + c;
+    *to = accumulate ? *to + sum : sum;
+  }
+}
+
+template <typename T>
+int moe_experts(const void* hidden, int ld_hidden, const void* w_in, const void* w_out,
+                const int* sorted, const int* tile_expert, int max_tiles, int top, int width,
+                int ff, float limit, float alpha, void* y, int ld_y, float* pair_out, int ld_out,
+                cudaStream_t stream) {
+  const dim3 grid_in(max_tiles, (ff + MOE_TN - 1) / MOE_TN);
+  int status = launch_kernel(moe_tile_kernel<T, 0>, grid_in, dim3(256), 0, stream, 1,
+                             (const T*)hidden, ld_hidden, (const T*)w_in, sorted, tile_expert,
+                             top, width, ff, limit, alpha, (T*)y, ld_y, (float*)nullptr, 0);
+  if (status != AYK_OK) return status;
+  const dim3 grid_out(max_tiles, (width + MOE_TN - 1) / MOE_TN);
+  return launch_kernel(moe_tile_kernel<T, 1>, grid_out, dim3(256), 0, stream, 1, (const T*)y,
+                       ld_y, (const T*)w_out, sorted, tile_expert, top, ff, width, limit, alpha,
+                       (T*)nullptr, 0, pair_out, ld_out);
+}
+
+}  // namespace ayk
+
+AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
+
+AYK_API int ayk_moe_tile_rows() { return ayk::MOE_TM; }
+
+AYK_API int ayk_moe_route(const float* logits, int ld, int rows, int experts, int top,
+                          int* chosen, float* share, void* stream) {
+  using namespace ayk;
+  if (rows == 0) return AYK_OK;
+  if (rows < 0 || experts < 1 || top < 1 || top > experts || ld < experts ||
+      logits == nullptr || chosen == nullptr || share == nullptr) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (experts > MOE_MAX_EXPERTS) return AYK_TOO_LARGE;
+  const int warps = 4;
+  return launch_kernel(moe_route_kernel, dim3((rows + warps - 1) / warps), dim3(32 * warps), 0,
+                       (cudaStream_t)stream, 1, logits, ld, rows, experts, top, chosen, share);
+}
+
+// Three launches: align, the two grouped products. `sorted` holds max_tiles * tile rows ints,
+// `tile_expert` max_tiles, `y` max_tiles * tile rows rows of ff, `pair_out` rows * top rows
+// of width. type: 0 = float32, 1 = bfloat16.
+AYK_API int ayk_moe_experts(const void* hidden, int ld_hidden, const void* w_in,
+                            const void* w_out, const int* chosen, int rows, int experts, int top,
+                            int width, int ff, float limit, float alpha, int* sorted,
+                            int* tile_expert, int max_tiles, void* y, int ld_y, float* pair_out,
+                            int ld_out, int type, void* stream) {
+  using namespace ayk;
+  if (rows == 0) return AYK_OK;
+  const long long pairs = (long long)rows * top;
+  if (rows < 0 || experts < 1 || top < 1 || width < 1 || ff < 1 || hidden == nullptr ||
+      w_in == nullptr || w_out == nullptr || chosen == nullptr || sorted == nullptr ||
+      tile_expert == nullptr || y == nullptr || pair_out == nullptr || ld_hidden < width ||
+      ld_y < ff || ld_out < width || !(limit > 0.f) ||
+      (long long)max_tiles * MOE_TM < pairs + (long long)min(experts, (int)pairs) * (MOE_TM - 1)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (experts > MOE_MAX_EXPERTS || max_tiles > 2000000) return AYK_TOO_LARGE;
+  cudaStream_t s = (cudaStream_t)stream;
+  int status = launch_kernel(moe_align_kernel, dim3(1), dim3(1024), 0, s, 1, chosen, (int)pairs,
+                             experts, max_tiles, sorted, tile_expert);
+  if (status != AYK_OK) return status;
+  if (type == 0) {
+    return moe_experts<float>(hidden, ld_hidden, w_in, w_out, sorted, tile_expert, max_tiles,
+                              top, width, ff, limit, alpha, y, ld_y, pair_out, ld_out, s);
+  }
+  if (type == 1) {
+    return moe_experts<__nv_bfloat16>(hidden, ld_hidden, w_in, w_out, sorted, tile_expert,
+                                      max_tiles, top, width, ff, limit, alpha, y, ld_y, pair_out,
+                                      ld_out, s);
+  }
+  return AYK_BAD_ARGUMENT;
+}
+
+AYK_API int ayk_moe_join(const float* pair_out, int ld, const float* share, int rows, int top,
+                         const float* scale, float* dst, int ld_dst, int width, int accumulate,
+                         void* stream) {
+  using namespace ayk;
+  if (rows == 0) return AYK_OK;
+  if (rows < 0 || top < 1 || width < 1 || pair_out == nullptr || share == nullptr ||
+      dst == nullptr || ld < width || ld_dst < width) {
+    return AYK_BAD_ARGUMENT;
+  }
+  const int threads = 256, tiles = min(8, (width + threads - 1) / threads);
+  return launch_kernel(moe_join_kernel, dim3(rows, tiles), dim3(threads), 0,
+                       (cudaStream_t)stream, 1, pair_out, ld, share, top, scale, dst, ld_dst,
+                       width, accumulate);
+}

@@ -416,6 +416,93 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int
   if (threadIdx.x == 0) *max_mine = m_run;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Gated linear attention with a decay per key channel: per head, with the raw decay z and
+// alpha = sigmoid(z)^(1/tau) = exp(logsigmoid(z) / tau),
+//   S <- diag(alpha) S + k v^T   (alpha_n scales row n of S: the entries of key channel n),
+//   out = S^T q * q_scale,       S: [N x P].
+// proj rows hold q at 0, k at k_offset (heads x N each) and v at v_offset (heads x P); z rows
+// hold heads x N raw decays. State of a slot: S as [heads][P][N]. The decays are turned into
+// factors in shared memory once per chunk, in fp32.
+template <int RN, int LANES>
+__global__ void __launch_bounds__(SCAN_COLS * LANES)
+gla_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int v_offset,
+                const float* __restrict__ z, int ld_z, float inv_tau, float q_scale,
+                float* __restrict__ state, long long state_stride,
+                const int* __restrict__ row_start, const int* __restrict__ state_slot,
+                float* __restrict__ out, int ld_out, int heads, int N, int P, int chunk,
+                int vec) {
+  extern __shared__ __align__(16) float scan_smem[];
+  const int stage_floats = chunk * (3 * N + SCAN_COLS);
+  pdl_launch_dependents();
+  const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * SCAN_COLS;
+  const int col = threadIdx.x / LANES, part = threadIdx.x % LANES;
+  const int p = p0 + col;
+  const int r0 = row_start[b], rows = row_start[b + 1] - r0;
+  if (state_slot[b] < 0) return;  // a row of padding (a graph's bucket): no request, no state
+  float* mine = state + (size_t)state_slot[b] * state_stride + (size_t)h * N * P;
+  pdl_wait_for(proj, z, mine);
+  float s[RN];
+#pragma unroll
+  for (int k = 0; k < RN; ++k) {
+    const int n = part + LANES * k;
+    s[k] = (p < P && n < N) ? mine[(size_t)p * N + n] : 0.f;
+  }
+  const int chunks = (rows + chunk - 1) / chunk;
+  auto stage = [&](int c) {
+    float* at = scan_smem + (size_t)(c % SCAN_STAGES) * stage_floats;
+    const int t0 = c * chunk, count = min(chunk, rows - t0);
+    const float* first = proj + (size_t)(r0 + t0) * ld_proj;
+    stage_tile(at, first + h * N, ld_proj, count, N, vec);                                  // q
+    stage_tile(at + (size_t)chunk * N, first + k_offset + h * N, ld_proj, count, N, vec);   // k
+    stage_tile(at + (size_t)2 * chunk * N, z + (size_t)(r0 + t0) * ld_z + h * N, ld_z, count, N,
+               vec);                                                                        // z
+    stage_columns(at + (size_t)3 * chunk * N, first + v_offset + h * P, ld_proj, count, p0, P,
+                  vec);                                                                     // v
+    copy_commit();
+  };
+  for (int c = 0; c < SCAN_STAGES - 1; ++c) {
+    if (c < chunks) stage(c); else copy_commit();
+  }
+  for (int c = 0; c < chunks; ++c) {
+    if (c + SCAN_STAGES - 1 < chunks) stage(c + SCAN_STAGES - 1); else copy_commit();
+    copy_wait<SCAN_STAGES - 1>();
+    __syncthreads();
+    float* q_s = scan_smem + (size_t)(c % SCAN_STAGES) * stage_floats;
+    float* k_s = q_s + (size_t)chunk * N;
+    float* a_s = k_s + (size_t)chunk * N;  // raw decays, then the factors
+    float* v_s = a_s + (size_t)chunk * N;
+    const int t0 = c * chunk, count = min(chunk, rows - t0);
+    for (int i = threadIdx.x; i < count * N; i += blockDim.x) {
+      a_s[i] = expf(log_sigmoid_f(a_s[i]) * inv_tau);
+    }
+    __syncthreads();
+    for (int i = 0; i < count; ++i) {
+      const float vv = v_s[i * SCAN_COLS + col];
+      const float* qi = q_s + (size_t)i * N;
+      const float* ki = k_s + (size_t)i * N;
+      const float* ai = a_s + (size_t)i * N;
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < RN; ++k) {
+        const int n = part + LANES * k;
+        if (n < N) {
+          s[k] = fmaf(ai[n], s[k], ki[n] * vv);
+          acc = fmaf(s[k], qi[n], acc);
+        }
+      }
+      const float sum = group_sum<LANES>(acc);
+      if (part == 0 && p < P) out[(size_t)(r0 + t0 + i) * ld_out + h * P + p] = sum * q_scale;
+    }
+    __syncthreads();  // the buffer is staged again at the next turn
+  }
+#pragma unroll
+  for (int k = 0; k < RN; ++k) {
+    const int n = part + LANES * k;
+    if (p < P && n < N) mine[(size_t)p * N + n] = s[k];
+  }
+}
+
 // rows of a chunk (at most 32: a warp scans a chunk's gates), and the ring's bytes: up to
 // 68 KB, which a kernel has to be allowed once (allow_smem)
 inline int scan_chunk(int n) { return n <= 64 ? 32 : (n <= 128 ? 16 : (n <= 256 ? 8 : 4)); }
@@ -543,4 +630,49 @@ AYK_API int ayk_mlstm_scan(const float* proj, int ld_proj, int k_offset, int v_o
   if (dim <= 256) AYK_MLSTM(8, 32, 1);
   AYK_MLSTM(16, 32, 1);
 #undef AYK_MLSTM
+}
+
+// rows of a chunk of the gated-linear-attention scan (three staged tiles of N entries a row)
+static inline int gla_chunk(int n) { return n <= 32 ? 32 : (n <= 64 ? 16 : (n <= 128 ? 8 : 4)); }
+
+AYK_API int ayk_gla_scan(const float* proj, int ld_proj, int k_offset, int v_offset,
+                         const float* z, int ld_z, float tau, float q_scale, float* state,
+                         long long state_stride, const int* row_start, const int* state_slot,
+                         float* out, int ld_out, int requests, int heads, int N, int P,
+                         void* stream) {
+  using namespace ayk;
+  if (requests == 0) return AYK_OK;
+  const int tiles = (P + SCAN_COLS - 1) / SCAN_COLS;
+  if (requests < 0 || heads < 1 || N < 1 || P < 1 || proj == nullptr || z == nullptr ||
+      state == nullptr || row_start == nullptr || state_slot == nullptr || out == nullptr ||
+      !(tau > 0.f) || ld_out < heads * P || ld_z < heads * N || requests > 65535 ||
+      ld_proj < max(k_offset + heads * N, v_offset + heads * P) ||
+      state_stride < (long long)heads * N * P) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (N > SCAN_MAX_N || tiles > 65535) return AYK_TOO_LARGE;
+  const int chunk = gla_chunk(N);
+  const size_t smem = (size_t)SCAN_STAGES * chunk * (3 * N + SCAN_COLS) * sizeof(float);
+  int vec = scan_vec(proj, ld_proj, N, P, {k_offset, v_offset});
+  if (((uintptr_t)z % 16) != 0 || ld_z % 4 != 0) vec = 1;
+  const dim3 grid(heads, requests, tiles);
+#define AYK_GLA(RN, LANES)                                                                     \
+  {                                                                                            \
+    static const bool allowed =                                                                \
+        (cudaFuncSetAttribute(gla_scan_kernel<RN, LANES>,                                      \
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024), true); \
+    (void)allowed;                                                                             \
+    return launch_kernel(gla_scan_kernel<RN, LANES>, grid, dim3(SCAN_COLS * LANES), smem,      \
+                         (cudaStream_t)stream, 1, proj, ld_proj, k_offset, v_offset, z, ld_z,  \
+                         1.f / tau, q_scale, state, state_stride, row_start, state_slot, out,  \
+                         ld_out, heads, N, P, chunk, vec);                                     \
+  }
+  if (N <= 8) AYK_GLA(1, 8);
+  if (N <= 16) AYK_GLA(2, 8);
+  if (N <= 32) AYK_GLA(4, 8);
+  if (N <= 64) AYK_GLA(4, 16);
+  if (N <= 128) AYK_GLA(4, 32);
+  if (N <= 256) AYK_GLA(8, 32);
+  AYK_GLA(16, 32);
+#undef AYK_GLA
 }

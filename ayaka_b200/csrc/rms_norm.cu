@@ -7,13 +7,22 @@
 //   GATE_SILU_BEFORE: x is first multiplied by silu(gate), then normalised (the gated norm of a
 //     state-space layer: the gate comes before the norm);
 //   GATE_SIGMOID_AFTER: the normalised, weighted value is multiplied by sigmoid(gate) (the
-//     output gate of a matrix-memory layer).
+//     output gate of a matrix-memory layer);
+//   GATE_SILU_AFTER: the normalised, weighted value is multiplied by silu(gate) (the output
+//     gate of a gated-linear-attention layer).
+// `weight_period` > 0: the weight has that many entries and repeats along the row (one weight
+// shared by every head).
+//
+// norm_sum: several fp32 rows of the same width, each normalised over the whole width with a
+// weight of its own, are averaged, multiplied element by element by an optional scale and
+// added to (or written into) an fp32 row: the join of mixers that run side by side.
 // Everything in fp32, rounded once to the output type. Any width.
 #include "common.cuh"
 
 namespace ayk {
 
-enum GateMode : int { GATE_NONE = 0, GATE_SILU_BEFORE = 1, GATE_SIGMOID_AFTER = 2 };
+enum GateMode : int { GATE_NONE = 0, GATE_SILU_BEFORE = 1, GATE_SIGMOID_AFTER = 2,
+                      GATE_SILU_AFTER = 3 };
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 
@@ -22,7 +31,7 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, int ld_x,
                                 const int* __restrict__ rows, const float* __restrict__ weight,
                                 float weight_offset, float eps, int group_width,
                                 const float* __restrict__ gate, int ld_gate, int gate_mode,
-                                TOut* __restrict__ out, int ld_out) {
+                                TOut* __restrict__ out, int ld_out, int weight_period) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   const int r = blockIdx.x, g = blockIdx.y;
@@ -41,7 +50,8 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, int ld_x,
     s += v * v;
   }
   const float inv = 1.f / sqrtf(block_sum(s, scratch) / (float)group_width + eps);
-  const float* w = weight + (size_t)g * group_width;
+  const float* w = weight_period > 0 ? weight : weight + (size_t)g * group_width;
+  const int w_first = weight_period > 0 ? (int)(((size_t)g * group_width) % weight_period) : 0;
   TOut* dst = out + (size_t)r * ld_out + (size_t)g * group_width;
   for (int c = threadIdx.x; c < group_width; c += blockDim.x) {
     float v = src[c];
@@ -49,28 +59,88 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, int ld_x,
       const float z = gt[c];
       v *= z * sigmoid_f(z);
     }
-    v = v * inv * (weight_offset + w[c]);
+    v = v * inv * (weight_offset + w[weight_period > 0 ? (w_first + c) % weight_period : c]);
     if (gate_mode == GATE_SIGMOID_AFTER) v *= sigmoid_f(gt[c]);
+    if (gate_mode == GATE_SILU_AFTER) {
+      const float z = gt[c];
+      v *= z * sigmoid_f(z);
+    }
     stf(dst + c, v);
+  }
+}
+
+// dst[r][c] (+)= scale[c] * x[r][c]
+__global__ void scale_add_kernel(const float* __restrict__ x, int ld_x,
+                                 const float* __restrict__ scale, float* __restrict__ dst,
+                                 int ld_dst, int width, int accumulate) {
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  pdl_wait_for(x, dst);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = x[(size_t)r * ld_x + c] * scale[c];
+    float* to = dst + (size_t)r * ld_dst + c;
+    *to = accumulate ? *to + v : v;
   }
 }
 
 template <typename TOut>
 int rms_norm(const float* x, int ld_x, const int* rows, const float* weight, float weight_offset,
              float eps, int groups, const float* gate, int ld_gate, int gate_mode, void* out,
-             int ld_out, int n, int width, cudaStream_t stream) {
+             int ld_out, int n, int width, int weight_period, cudaStream_t stream) {
   if (n == 0) return AYK_OK;
   if (n < 0 || width < 1 || groups < 1 || width % groups || ld_x < width || ld_out < width ||
       !(eps > 0.f) || weight == nullptr || gate_mode < GATE_NONE ||
-      gate_mode > GATE_SIGMOID_AFTER || ((gate_mode != GATE_NONE) != (gate != nullptr)) ||
-      (gate != nullptr && ld_gate < width)) {
+      gate_mode > GATE_SILU_AFTER || ((gate_mode != GATE_NONE) != (gate != nullptr)) ||
+      (gate != nullptr && ld_gate < width) || weight_period < 0) {
     return AYK_BAD_ARGUMENT;
   }
   const int group_width = width / groups;
   const int threads = group_width >= 2048 ? 512 : (group_width >= 512 ? 256 : 128);
   return launch_kernel(rms_norm_kernel<TOut>, dim3(n, groups), dim3(threads), 0, stream, 1, x,
                        ld_x, rows, weight, weight_offset, eps, group_width, gate, ld_gate,
-                       gate_mode, (TOut*)out, ld_out);
+                       gate_mode, (TOut*)out, ld_out, weight_period);
+}
+
+constexpr int SUM_MAX_BRANCHES = 4;
+struct Branches {
+  const float* x[SUM_MAX_BRANCHES];
+  const float* weight[SUM_MAX_BRANCHES];
+  int ld[SUM_MAX_BRANCHES];
+};
+
+// dst[r][c] (+)= scale[c] * factor * sum_b x_b[r][c] * rsqrt(mean_c(x_b[r]^2) + eps) * w_b[c]
+__global__ void norm_sum_kernel(Branches in, int count, float eps, float factor,
+                                const float* __restrict__ scale, float* __restrict__ dst,
+                                int ld_dst, int width, int accumulate) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  pdl_wait_for(dst);
+  float inv[SUM_MAX_BRANCHES];
+#pragma unroll
+  for (int b = 0; b < SUM_MAX_BRANCHES; ++b) {
+    inv[b] = 0.f;
+    if (b < count) {
+      const float* src = in.x[b] + (size_t)r * in.ld[b];
+      float s = 0.f;
+      for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = src[c];
+        s += v * v;
+      }
+      inv[b] = 1.f / sqrtf(block_sum(s, scratch) / (float)width + eps);
+    }
+  }
+  float* to = dst + (size_t)r * ld_dst;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float sum = 0.f;
+#pragma unroll
+    for (int b = 0; b < SUM_MAX_BRANCHES; ++b) {
+      if (b < count) sum += in.x[b][(size_t)r * in.ld[b] + c] * inv[b] * in.weight[b][c];
+    }
+    sum *= factor;
+    if (scale != nullptr) sum *= scale[c];
+    to[c] = accumulate ? to[c] + sum : sum;
+  }
 }
 
 }  // namespace ayk
@@ -81,15 +151,51 @@ AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 AYK_API int ayk_rms_norm(const float* x, int ld_x, const int* rows, const float* weight,
                          float weight_offset, float eps, int groups, const float* gate,
                          int ld_gate, int gate_mode, void* out, int ld_out, int n, int width,
-                         int out_type, void* stream) {
+                         int out_type, int weight_period, void* stream) {
   if (out_type == 0) {
     return ayk::rms_norm<float>(x, ld_x, rows, weight, weight_offset, eps, groups, gate, ld_gate,
-                                gate_mode, out, ld_out, n, width, (cudaStream_t)stream);
+                                gate_mode, out, ld_out, n, width, weight_period,
+                                (cudaStream_t)stream);
   }
   if (out_type == 1) {
     return ayk::rms_norm<__nv_bfloat16>(x, ld_x, rows, weight, weight_offset, eps, groups, gate,
-                                        ld_gate, gate_mode, out, ld_out, n, width,
+                                        ld_gate, gate_mode, out, ld_out, n, width, weight_period,
                                         (cudaStream_t)stream);
   }
   return AYK_BAD_ARGUMENT;
+}
+
+// `count` rows x[b] (fp32, leading dimension ld[b]) with weights w[b]; `scale` may be null.
+AYK_API int ayk_norm_sum(const float* const* x, const int* ld, const float* const* weight,
+                         int count, float eps, float factor, const float* scale, float* dst,
+                         int ld_dst, int n, int width, int accumulate, void* stream) {
+  using namespace ayk;
+  if (n == 0) return AYK_OK;
+  if (n < 0 || width < 1 || count < 1 || x == nullptr || ld == nullptr || weight == nullptr ||
+      dst == nullptr || ld_dst < width || !(eps > 0.f)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (count > SUM_MAX_BRANCHES) return AYK_TOO_LARGE;
+  Branches in = {};
+  for (int b = 0; b < count; ++b) {
+    if (x[b] == nullptr || weight[b] == nullptr || ld[b] < width) return AYK_BAD_ARGUMENT;
+    in.x[b] = x[b];
+    in.weight[b] = weight[b];
+    in.ld[b] = ld[b];
+  }
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  return launch_kernel(norm_sum_kernel, dim3(n), dim3(threads), 0, (cudaStream_t)stream, 1, in,
+                       count, eps, factor, scale, dst, ld_dst, width, accumulate);
+}
+
+AYK_API int ayk_scale_add(const float* x, int ld_x, const float* scale, float* dst, int ld_dst,
+                          int n, int width, int accumulate, void* stream) {
+  using namespace ayk;
+  if (n == 0) return AYK_OK;
+  if (n < 0 || width < 1 || x == nullptr || scale == nullptr || dst == nullptr ||
+      ld_x < width || ld_dst < width) {
+    return AYK_BAD_ARGUMENT;
+  }
+  return launch_kernel(scale_add_kernel, dim3(n), dim3(width >= 512 ? 256 : 128), 0,
+                       (cudaStream_t)stream, 1, x, ld_x, scale, dst, ld_dst, width, accumulate);
 }

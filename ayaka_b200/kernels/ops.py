@@ -9,6 +9,7 @@ library or a refused argument raises :class:`~ayaka_b200.errors.BackendError`.
 from __future__ import annotations
 
 import contextlib
+import math
 from collections.abc import Iterator
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
@@ -33,6 +34,7 @@ __all__ = [
     "latent_prepare",
     "launch_count",
     "leaving_out",
+    "gla_scan",
     "layer_norm",
     "linear",
     "linear_normed",
@@ -40,14 +42,22 @@ __all__ = [
     "logits_scale_cap",
     "mamba2_scan",
     "mlstm_scan",
+    "moe_experts",
+    "moe_join",
+    "moe_max_tiles",
+    "moe_route",
+    "norm_sum",
     "rms_norm",
     "rope",
     "rope_frequencies",
     "sample",
+    "scale_add",
     "scan_state_floats",
     "set_decode_tensor_cores",
     "set_pdl",
     "sm_count",
+    "talking_attention",
+    "talking_prepare",
     "timed",
 ]
 
@@ -89,7 +99,8 @@ _TIMED = ("embed_rows", "layer_norm", "linear", "linear_kv", "kv_store", "attent
           "attention_prefill", "attention_decode", "argmax", "sample", "rms_norm", "rope",
           "latent_prepare", "head_linear", "latent_attention", "latent_decode",
           "causal_conv_silu", "mamba2_scan",
-          "mlstm_scan")
+          "mlstm_scan", "gla_scan", "talking_prepare", "talking_attention", "norm_sum",
+          "moe_route", "moe_experts", "moe_join")
 
 
 @contextlib.contextmanager
@@ -698,7 +709,7 @@ def logits_adjust(logits: torch.Tensor, desc: torch.Tensor, num_rows: int,
 
 # ---- norms by the root mean square, rotations ---------------------------------------------
 
-GATES = {"none": 0, "silu_before": 1, "sigmoid_after": 2}
+GATES = {"none": 0, "silu_before": 1, "sigmoid_after": 2, "silu_after": 3}
 ROPE_LAYOUTS = {"neighbours": 0, "halves": 1}
 
 
@@ -711,7 +722,9 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
 
     With ``rows`` (int32), output row ``i`` normalises ``x[rows[i]]``. With ``gate`` (float32,
     laid out like ``x``): ``gate_mode="silu_before"`` multiplies ``x`` by ``silu(gate)`` before
-    the norm, ``"sigmoid_after"`` multiplies the result by ``sigmoid(gate)``.
+    the norm, ``"sigmoid_after"`` multiplies the result by ``sigmoid(gate)``, ``"silu_after"``
+    by ``silu(gate)``. A ``weight`` shorter than a row repeats along it (its length must divide
+    a group's width: one weight shared by every head).
     """
     op = "rms_norm"
     if _left_out and op in _left_out:
@@ -721,8 +734,10 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
     _need(op, "out", out, ndim=2)
     if out.dtype not in _TYPE:
         raise BackendError(f"{op}: out must be float32 or bfloat16, got {out.dtype}")
-    width = weight.shape[0]
-    if x.shape[1] != width or out.shape[1] != width or groups < 1 or width % groups:
+    width = out.shape[1]
+    period = 0 if weight.shape[0] == width else weight.shape[0]
+    if x.shape[1] != width or groups < 1 or width % groups or \
+            (period and (width // groups) % period):
         raise BackendError(f"{op}: widths differ or {groups} groups do not divide {width}")
     if gate_mode not in GATES or (gate is None) != (gate_mode == "none"):
         raise BackendError(f"{op}: gate and gate_mode {gate_mode!r} do not go together")
@@ -740,14 +755,31 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
         _ptr(x), c_int(x.stride(0)), _ptr(rows), _ptr(weight), c_float(weight_offset),
         c_float(eps), c_int(groups), _ptr(gate), c_int(0 if gate is None else gate.stride(0)),
         c_int(GATES[gate_mode]), _ptr(out), c_int(out.stride(0)), c_int(n), c_int(width),
-        c_int(_TYPE[out.dtype]), _stream())
+        c_int(_TYPE[out.dtype]), c_int(period), _stream())
     check(status, op)
 
 
-def rope_frequencies(dims: int, base: float, device: torch.device) -> torch.Tensor:
+def rope_frequencies(dims: int, base: float, device: torch.device,
+                     scaling: tuple[float, float, float, int] | None = None) -> torch.Tensor:
     """``f_i = base^(-2i / dims)`` for the ``dims / 2`` pairs, as float64 on ``device`` (the
-    kernels form ``position * f_i`` and its sine and cosine in double precision)."""
-    values = [float(base) ** (-2.0 * i / dims) for i in range(dims // 2)]
+    kernels form ``position * f_i`` and its sine and cosine in double precision).
+
+    ``scaling = (factor, low, high, original)`` rescales by wavelength ``l = 2 pi / f``: a
+    pair with ``l > original / low`` turns ``factor`` times slower, one with ``l < original /
+    high`` is kept, and between the two the slowed and the kept frequency are blended with
+    the weight ``(original / l - low) / (high - low)`` on the kept one."""
+    values = []
+    for i in range(dims // 2):
+        f = float(base) ** (-2.0 * i / dims)
+        if scaling is not None:
+            factor, low, high, original = scaling
+            wavelength = 2.0 * math.pi / f
+            if wavelength > original / low:
+                f = f / factor
+            elif wavelength >= original / high:
+                keep = (original / wavelength - low) / (high - low)
+                f = (1.0 - keep) * f / factor + keep * f
+        values.append(f)
     return torch.tensor(values, dtype=torch.float64, device=device)
 
 
@@ -1081,4 +1113,297 @@ def mlstm_scan(proj: torch.Tensor, gate_bias: torch.Tensor | None, state: torch.
         c_longlong(state.stride(0)), _ptr(row_start), _ptr(state_slot), _ptr(out),
         c_int(out.stride(0)), c_int(requests), c_int(heads), c_int(dim), c_int(columns),
         _stream())
+    check(status, op)
+
+
+def gla_scan(proj: torch.Tensor, decay_raw: torch.Tensor, state: torch.Tensor,
+             out: torch.Tensor, *, row_start: torch.Tensor, state_slot: torch.Tensor,
+             requests: int, heads: int, dim: int, columns: int, k_offset: int, v_offset: int,
+             tau: float, q_scale: float) -> None:
+    """Gated linear attention with a decay per key channel over each request's rows. ``proj``
+    float32 rows hold the queries at 0, keys at ``k_offset`` (``heads * dim`` each) and values
+    at ``v_offset`` (``heads * columns``); ``decay_raw`` ``[N, heads * dim]`` the raw decays
+    ``z``. Per head ``S <- diag(sigmoid(z)^(1/tau)) S + k v^T`` (the decay of key channel ``n``
+    on row ``n`` of ``S``) and ``out = q_scale * S^T q``. ``state`` ``[slots, heads * dim *
+    columns]`` float32, a slot's ``S`` kept as ``[heads][columns][dim]``."""
+    op = "gla_scan"
+    if _left_out and op in _left_out:
+        return
+    for name, tensor in (("proj", proj), ("decay_raw", decay_raw), ("state", state),
+                         ("out", out)):
+        _need(op, name, tensor, torch.float32, 2)
+    if state.shape[1] < heads * dim * columns or out.shape[1] != heads * columns or \
+            decay_raw.shape[1] != heads * dim or \
+            proj.shape[1] < max(k_offset + heads * dim, v_offset + heads * columns):
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("recurrent").ayk_gla_scan(
+        _ptr(proj), c_int(proj.stride(0)), c_int(k_offset), c_int(v_offset), _ptr(decay_raw),
+        c_int(decay_raw.stride(0)), c_float(tau), c_float(q_scale), _ptr(state),
+        c_longlong(state.stride(0)), _ptr(row_start), _ptr(state_slot), _ptr(out),
+        c_int(out.stride(0)), c_int(requests), c_int(heads), c_int(dim), c_int(columns),
+        _stream())
+    check(status, op)
+
+
+# ---- attention with mixed heads, mixers side by side ----------------------------------------
+
+def talking_prepare(proj: torch.Tensor, *, k_offset: int, v_offset: int,
+                    bias: torch.Tensor | None, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
+                    positions: torch.Tensor, freq: torch.Tensor | None, layout: str,
+                    talk: torch.Tensor | None, temp: torch.Tensor | None, scale: float,
+                    slot_mapping: torch.Tensor | None, k_pages: torch.Tensor | None,
+                    v_pages: torch.Tensor | None, qmix: torch.Tensor, heads: int, kv_heads: int,
+                    dim: int, vdim: int, rows: int) -> None:
+    """From a row of a fused projection (float32: ``heads * dim`` queries at 0, ``kv_heads *
+    dim`` keys at ``k_offset``, ``kv_heads * vdim`` values at ``v_offset``): queries and keys
+    each normalised by the root mean square over their whole projection with a weight per
+    entry (``q_weight`` / ``k_weight``; ``None``: no norm) after ``bias`` (float32, laid out as
+    the projection's query, key and value columns; optional) is added, the first ``2 * len(freq)`` entries
+    of every head rotated by the position, the key and value stored into the row's cache
+    slot (``k_pages`` ``[page, kv_head, slot, dim]``, ``v_pages`` likewise with ``vdim``), and
+    the *mixed queries* written to ``qmix`` ``[N, heads * kv_heads * dim]``:
+    ``m[h, g] = sum over heads a of group g of talk[h, a] * temp[a] * scale * q[a]``, so that
+    head ``h``'s mixed score against a token is ``sum_g m[h, g] . k[g]``."""
+    op = "talking_prepare"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "proj", proj, torch.float32, 2)
+    _need(op, "positions", positions, torch.int32, 1)
+    _need(op, "qmix", qmix, ndim=2)
+    if qmix.dtype not in _TYPE or layout not in ROPE_LAYOUTS:
+        raise BackendError(f"{op}: float32 or bfloat16 and a known layout only")
+    for name, tensor, size in (("bias", bias, v_offset + kv_heads * vdim),
+                               ("q_weight", q_weight, heads * dim),
+                               ("k_weight", k_weight, kv_heads * dim),
+                               ("talk", talk, heads * heads), ("temp", temp, heads)):
+        if tensor is not None:
+            _need(op, name, tensor, torch.float32)
+            if tensor.numel() != size or not tensor.is_contiguous():
+                raise BackendError(f"{op}: {name} must hold {size} contiguous entries")
+    page_size = 1
+    if k_pages is not None:
+        if v_pages is None or slot_mapping is None:
+            raise BackendError(f"{op}: key pages come with value pages and a slot mapping")
+        _need(op, "k_pages", k_pages, qmix.dtype, 4)
+        _need(op, "v_pages", v_pages, qmix.dtype, 4)
+        _need(op, "slot_mapping", slot_mapping, torch.int32, 1)
+        page_size = k_pages.shape[2]
+        if tuple(k_pages.shape[1:]) != (kv_heads, page_size, dim) or \
+                tuple(v_pages.shape[1:]) != (kv_heads, page_size, vdim) or \
+                not k_pages.is_contiguous() or not v_pages.is_contiguous() or \
+                rows > slot_mapping.shape[0]:
+            raise BackendError(f"{op}: pages must be contiguous [page, kv_head, slot, dim]")
+    rot_dims = 0
+    if freq is not None and freq.numel():
+        _need(op, "freq", freq, torch.float64, 1)
+        rot_dims = 2 * freq.shape[0]
+    if rows > proj.shape[0] or rows > positions.shape[0] or rows > qmix.shape[0] or \
+            qmix.shape[1] != heads * kv_heads * dim or \
+            proj.shape[1] < v_offset + kv_heads * vdim:
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("talking_attention").ayk_talking_prepare(
+        _ptr(proj), c_int(proj.stride(0)), c_int(k_offset), c_int(v_offset), _ptr(bias),
+        _ptr(q_weight), _ptr(k_weight), c_float(eps), _ptr(positions), _ptr(freq if rot_dims else None),
+        c_int(rot_dims), c_int(ROPE_LAYOUTS[layout]), _ptr(talk), _ptr(temp), c_float(scale),
+        _ptr(slot_mapping if k_pages is not None else None), _ptr(k_pages), _ptr(v_pages),
+        c_int(page_size), _ptr(qmix), c_int(qmix.stride(0)), c_int(rows), c_int(heads),
+        c_int(kv_heads), c_int(dim), c_int(vdim), c_int(_TYPE[qmix.dtype]), _stream())
+    check(status, op)
+
+
+def talking_attention(qmix: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      block_table: torch.Tensor, request_of_row: torch.Tensor,
+                      positions: torch.Tensor, out: torch.Tensor, *, heads: int, chunk: int = 0,
+                      window: int = 0, reach: int, gate: torch.Tensor | None = None,
+                      rows: int | None = None) -> None:
+    """Softmax attention of mixed queries (see :func:`talking_prepare`; every factor is in
+    them) over paged keys and values. The row of request ``request_of_row[i]`` at
+    ``positions[i]`` sees the keys from the start of its block of ``chunk`` positions
+    (``chunk`` 0: from 0), and no further back than ``window`` (0: no limit), up to itself;
+    head ``h`` sums the values of key/value head ``h // (heads / kv_heads)``; with ``gate``
+    (float32 ``[N, heads]``) its result is multiplied by ``sigmoid(gate[:, h])``. ``reach``
+    bounds the keys any row sees. The step's own keys must already be stored."""
+    op = "talking_attention"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "qmix", qmix, ndim=2)
+    _need(op, "out", out, qmix.dtype, 2)
+    _need(op, "k_pages", k_pages, qmix.dtype, 4)
+    _need(op, "v_pages", v_pages, qmix.dtype, 4)
+    _need(op, "block_table", block_table, torch.int32, 2)
+    _need(op, "request_of_row", request_of_row, torch.int32, 1)
+    _need(op, "positions", positions, torch.int32, 1)
+    if qmix.dtype not in _TYPE or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise BackendError(f"{op}: contiguous float32 or bfloat16 pages only")
+    _, kv_heads, page_size, dim = k_pages.shape
+    vdim = v_pages.shape[3]
+    n = qmix.shape[0] if rows is None else rows
+    if qmix.shape[1] != heads * kv_heads * dim or out.shape[1] != heads * vdim or \
+            tuple(v_pages.shape[:3]) != tuple(k_pages.shape[:3]) or n > out.shape[0] or \
+            n > request_of_row.shape[0] or n > positions.shape[0] or heads % kv_heads:
+        raise BackendError(f"{op}: shapes do not fit")
+    if gate is not None:
+        _need(op, "gate", gate, torch.float32, 2)
+        if gate.shape[1] != heads or gate.shape[0] < n:
+            raise BackendError(f"{op}: the gate does not match the rows")
+    status = library("talking_attention").ayk_talking_attention(
+        _ptr(qmix), c_int(qmix.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+        c_int(block_table.stride(0)), _ptr(request_of_row), _ptr(positions), _ptr(gate),
+        c_int(0 if gate is None else gate.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(n),
+        c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(page_size), c_int(chunk),
+        c_int(window), c_int(max(1, reach)), c_int(_TYPE[qmix.dtype]), _stream())
+    check(status, op)
+
+
+def norm_sum(branches: list[torch.Tensor], weights: list[torch.Tensor], eps: float,
+             dst: torch.Tensor, *, factor: float, scale: torch.Tensor | None = None,
+             accumulate: bool = True, rows: int) -> None:
+    """``dst (+)= scale * factor * sum_b rms_norm(branches[b]) * weights[b]``: up to four
+    float32 ``[N, width]`` results, each normalised over the whole width by its root mean
+    square with its own weight, summed, multiplied element by element by ``scale`` (float32
+    ``[width]``, optional) and added to (``accumulate``) or written into float32 ``dst``."""
+    op = "norm_sum"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "dst", dst, torch.float32, 2)
+    width = dst.shape[1]
+    if len(branches) != len(weights) or not 1 <= len(branches) <= 4 or rows > dst.shape[0]:
+        raise BackendError(f"{op}: one weight per branch, one to four branches")
+    for branch, weight in zip(branches, weights):
+        _need(op, "branch", branch, torch.float32, 2)
+        _need(op, "weight", weight, torch.float32, 1)
+        if branch.shape[1] != width or weight.shape[0] != width or rows > branch.shape[0]:
+            raise BackendError(f"{op}: widths differ")
+    if scale is not None:
+        _need(op, "scale", scale, torch.float32, 1)
+        if scale.shape[0] != width:
+            raise BackendError(f"{op}: the scale does not match the width")
+    count = len(branches)
+    xs = (c_void_p * count)(*[b.data_ptr() for b in branches])
+    ws = (c_void_p * count)(*[w.data_ptr() for w in weights])
+    lds = (c_int * count)(*[b.stride(0) for b in branches])
+    status = library("rms_norm").ayk_norm_sum(
+        xs, lds, ws, c_int(count), c_float(eps), c_float(factor), _ptr(scale), _ptr(dst),
+        c_int(dst.stride(0)), c_int(rows), c_int(width), c_int(1 if accumulate else 0),
+        _stream())
+    check(status, op)
+
+
+def scale_add(x: torch.Tensor, scale: torch.Tensor, dst: torch.Tensor, *, rows: int,
+              accumulate: bool = True) -> None:
+    """``dst (+)= scale * x`` over float32 rows, ``scale`` a float32 vector of the width."""
+    op = "scale_add"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "x", x, torch.float32, 2)
+    _need(op, "scale", scale, torch.float32, 1)
+    _need(op, "dst", dst, torch.float32, 2)
+    width = dst.shape[1]
+    if x.shape[1] != width or scale.shape[0] != width or rows > x.shape[0] or \
+            rows > dst.shape[0]:
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("rms_norm").ayk_scale_add(
+        _ptr(x), c_int(x.stride(0)), _ptr(scale), _ptr(dst), c_int(dst.stride(0)), c_int(rows),
+        c_int(width), c_int(1 if accumulate else 0), _stream())
+    check(status, op)
+
+
+# ---- mixture of experts ---------------------------------------------------------------------
+
+#: pairs (row, chosen expert) per tile of the grouped products (``MOE_TM`` in ``csrc/moe.cu``)
+MOE_TILE_ROWS = 32
+
+
+def moe_max_tiles(rows: int, experts: int, top: int) -> int:
+    """Tiles the grouped products may need for ``rows`` rows: every expert's pairs are padded
+    to whole tiles."""
+    pairs = rows * top
+    return -(-(pairs + min(experts, pairs) * (MOE_TILE_ROWS - 1)) // MOE_TILE_ROWS)
+
+
+def moe_route(logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor, *, top: int,
+              rows: int) -> None:
+    """Per row of float32 ``logits`` ``[N, experts]``: the ``top`` largest (ties to the smaller
+    index), in descending order, into ``chosen`` (int32 ``[N * top]``), and the softmax over
+    just those into ``share`` (float32 ``[N * top]``)."""
+    op = "moe_route"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "logits", logits, torch.float32, 2)
+    _need(op, "chosen", chosen, torch.int32, 1)
+    _need(op, "share", share, torch.float32, 1)
+    if rows > logits.shape[0] or min(chosen.shape[0], share.shape[0]) < rows * top:
+        raise BackendError(f"{op}: shapes do not fit")
+    status = library("moe").ayk_moe_route(
+        _ptr(logits), c_int(logits.stride(0)), c_int(rows), c_int(logits.shape[1]), c_int(top),
+        _ptr(chosen), _ptr(share), _stream())
+    check(status, op)
+
+
+def moe_experts(hidden: torch.Tensor, w_in: torch.Tensor, w_out: torch.Tensor,
+                chosen: torch.Tensor, pair_out: torch.Tensor, *, experts: int, top: int,
+                limit: float, alpha: float, sorted_pairs: torch.Tensor,
+                tile_expert: torch.Tensor, inner: torch.Tensor, rows: int) -> None:
+    """The chosen experts of every row, as two products grouped by expert. ``w_in``
+    ``[experts * 2 * ff, width]`` holds each expert's gate rows, then its up rows; ``w_out``
+    ``[experts * width, ff]`` its down matrix. Pair ``p = row * top + choice`` computes
+    ``g = min(W_gate h, limit)``, ``u = clamp(W_up h, -limit, limit)``,
+    ``y = g * sigmoid(alpha * g) * (u + 1)`` and ``pair_out[p] = W_down y`` (float32
+    ``[N * top, width]``, unweighted). Scratch: ``sorted_pairs`` (int32, ``tiles * tile
+    rows``), ``tile_expert`` (int32, ``tiles``) and ``inner`` (``[tiles * tile rows, ff]``,
+    compute dtype) for ``tiles = moe_max_tiles(rows, experts, top)``."""
+    op = "moe_experts"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "hidden", hidden, ndim=2)
+    _need(op, "w_in", w_in, hidden.dtype, 2)
+    _need(op, "w_out", w_out, hidden.dtype, 2)
+    _need(op, "inner", inner, hidden.dtype, 2)
+    _need(op, "chosen", chosen, torch.int32, 1)
+    _need(op, "pair_out", pair_out, torch.float32, 2)
+    _need(op, "sorted_pairs", sorted_pairs, torch.int32, 1)
+    _need(op, "tile_expert", tile_expert, torch.int32, 1)
+    width, ff = hidden.shape[1], w_out.shape[1]
+    tiles = moe_max_tiles(rows, experts, top)
+    if hidden.dtype not in _TYPE or not w_in.is_contiguous() or not w_out.is_contiguous() or \
+            tuple(w_in.shape) != (experts * 2 * ff, width) or \
+            tuple(w_out.shape) != (experts * width, ff) or inner.shape[1] != ff or \
+            pair_out.shape[1] != width or rows > hidden.shape[0] or \
+            chosen.shape[0] < rows * top or pair_out.shape[0] < rows * top or \
+            sorted_pairs.shape[0] < tiles * MOE_TILE_ROWS or tile_expert.shape[0] < tiles or \
+            inner.shape[0] < tiles * MOE_TILE_ROWS:
+        raise BackendError(f"{op}: shapes do not fit")
+    global _launches
+    _launches += 2  # align and two products
+    status = library("moe").ayk_moe_experts(
+        _ptr(hidden), c_int(hidden.stride(0)), _ptr(w_in), _ptr(w_out), _ptr(chosen),
+        c_int(rows), c_int(experts), c_int(top), c_int(width), c_int(ff), c_float(limit),
+        c_float(alpha), _ptr(sorted_pairs), _ptr(tile_expert), c_int(tiles), _ptr(inner),
+        c_int(inner.stride(0)), _ptr(pair_out), c_int(pair_out.stride(0)),
+        c_int(_TYPE[hidden.dtype]), _stream())
+    check(status, op)
+
+
+def moe_join(pair_out: torch.Tensor, share: torch.Tensor, dst: torch.Tensor, *, top: int,
+             scale: torch.Tensor | None = None, accumulate: bool = True, rows: int) -> None:
+    """``dst[row] (+)= scale * sum_j share[row * top + j] * pair_out[row * top + j]`` in
+    float32, the choices in order; ``scale`` (float32 ``[width]``) is optional."""
+    op = "moe_join"
+    if _left_out and op in _left_out:
+        return
+    _need(op, "pair_out", pair_out, torch.float32, 2)
+    _need(op, "share", share, torch.float32, 1)
+    _need(op, "dst", dst, torch.float32, 2)
+    width = dst.shape[1]
+    if pair_out.shape[1] != width or pair_out.shape[0] < rows * top or \
+            share.shape[0] < rows * top or rows > dst.shape[0]:
+        raise BackendError(f"{op}: shapes do not fit")
+    if scale is not None:
+        _need(op, "scale", scale, torch.float32, 1)
+        if scale.shape[0] != width:
+            raise BackendError(f"{op}: the scale does not match the width")
+    status = library("moe").ayk_moe_join(
+        _ptr(pair_out), c_int(pair_out.stride(0)), _ptr(share), c_int(rows), c_int(top),
+        _ptr(scale), _ptr(dst), c_int(dst.stride(0)), c_int(width),
+        c_int(1 if accumulate else 0), _stream())
     check(status, op)

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from collections.abc import Mapping
+from collections.abc import Callable, Mapping
 from pathlib import Path
 
 import torch
@@ -21,10 +21,15 @@ _DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
 def build_model(config_json: Mapping[str, object], dtype: str,
-                device: str | torch.device) -> tuple[DecoderModel, Architecture, object]:
-    """Build (not load) the model a parsed ``config.json`` names."""
+                device: str | torch.device,
+                shape_of: Callable[[str], tuple[int, ...] | None] | None = None
+                ) -> tuple[DecoderModel, Architecture, object]:
+    """Build (not load) the model a parsed ``config.json`` names. ``shape_of`` gives the
+    shape of a checkpoint tensor (or ``None``) to a design that leaves a size to them."""
     architecture = architecture_of(config_json)
     config = architecture.parse_config(config_json)
+    if architecture.complete_config is not None and shape_of is not None:
+        config = architecture.complete_config(config, shape_of)
     ctx = BuildContext(dtype=_DTYPES[dtype], device=torch.device(device))
     return DecoderModel(architecture.model_spec(config), ctx), architecture, config
 
@@ -34,9 +39,14 @@ def load_model(model_dir: str | Path, dtype: str, device: str | torch.device,
     """Build the model of ``model_dir/config.json`` and fill it from the folder's
     safetensors (or from ``tensors``, checkpoint-named, when given)."""
     config_json = read_config_json(model_dir)
-    model, architecture, config = build_model(config_json, dtype, device)
     source = TensorSource(tensors=tensors) if tensors is not None else open_model_dir(model_dir)
+    known = set(source.names())
+
+    def shape_of(name: str) -> tuple[int, ...] | None:
+        return tuple(source.describe(name)[0]) if name in known else None
+
     try:
+        model, architecture, config = build_model(config_json, dtype, device, shape_of)
         load_into(model, architecture.weight_rules(config), source)
     finally:
         source.close()

@@ -33,6 +33,11 @@ class Architecture:
     weight_rules: Callable[[object], WeightRules]
     random_tensors: Callable[[object, int, RandomInit], Iterator[tuple[str, torch.Tensor]]]
     config_json: Callable[[object], dict[str, object]]
+    #: for a design whose ``config.json`` leaves a size to the stored tensors:
+    #: ``(config, shape_of)`` -> the configuration with that size filled in, where
+    #: ``shape_of(name)`` is the shape of a checkpoint tensor or ``None``
+    complete_config: Callable[[object, Callable[[str], tuple[int, ...] | None]], object] \
+        | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
@@ -74,4 +79,5 @@ def architecture_of(config_json: Mapping[str, object]) -> Architecture:
 
 def _builtin() -> None:
     import ayaka_b200.models.gpt2  # noqa: F401  (registers itself)
+    import ayaka_b200.models.gagotar  # noqa: F401
     import ayaka_b200.models.mapuvik  # noqa: F401

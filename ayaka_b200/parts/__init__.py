@@ -1,13 +1,14 @@
 """The parts a model is put together from, each registered under a kind name.
 
 Importing this package registers the built-in kinds: mixers ``attention``,
-``latent_attention``, ``mamba2`` and ``mlstm``; feed-forwards ``dense`` and ``none``; norms
+``latent_attention``, ``mamba2``, ``mlstm``, ``gated_linear_attention``, ``talking_attention``
+and ``side_by_side``; feed-forwards ``dense``, ``experts`` and ``none``; norms
 ``layer_norm`` and ``rms_norm``; positions ``learned``, ``rotary`` and ``none``; blocks
 ``pre_norm`` and ``parallel``; embedding ``token``; head ``linear``.
 """
 
-from ayaka_b200.parts import (block, embedding, feed_forward, latent, mixer, norm,  # noqa: F401
-                              recurrent)
+from ayaka_b200.parts import (block, embedding, experts, feed_forward, latent,  # noqa: F401
+                              mixer, norm, recurrent, side_by_side)
 from ayaka_b200.parts.base import (BuildContext, CacheNeed, Part, StateNeed, build_part,
                                    register_part, registered_kinds)
 from ayaka_b200.parts.context import GroupStep, LayerCache, StepContext, Workspace

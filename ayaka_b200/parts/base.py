@@ -43,6 +43,17 @@ class CacheNeed:
     head_dim: int
     window: int = 0  # 0: every earlier key; n > 0: the last n keys
     values: bool = True  # False: one row per token only (a latent cache): no value pages
+    chunk: int = 0  # n > 0: only keys of the query's own block of n positions (from 0)
+    value_dim: int = 0  # entries of a value row when they differ from a key's (0: head_dim)
+
+    @property
+    def value_head_dim(self) -> int:
+        return self.value_dim or self.head_dim
+
+    @property
+    def forgets(self) -> bool:
+        """Whether pages fall out of every later row's sight (a window or blocks)."""
+        return self.window > 0 or self.chunk > 0
 
 
 @dataclass(frozen=True, slots=True)

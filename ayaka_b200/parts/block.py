@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import torch
 
+from ayaka_b200.kernels import ops
 from ayaka_b200.parts.base import BuildContext, Part, build_part, register_part
 from ayaka_b200.parts.context import LayerCache, StepContext, Workspace
 from ayaka_b200.parts.spec import LayerSpec
@@ -25,7 +26,13 @@ class Block(Part):
 class PreNormBlock(Block):
     """``x += mixer(norm(x)); x += feed_forward(norm(x))`` — GPT-2's block
     (``python/ayaka/models/gpt2.py:99-101``). The sums happen in fp32 inside the last matrix
-    product of each half."""
+    product of each half.
+
+    With ``spec.layer_scale`` each half's result is multiplied element by element by a vector
+    of the model's width (``mixer_scale``, ``feed_forward_scale``) before the sum: a part that
+    has ``forward_scaled(hidden, residual, step[, cache], scale)`` applies the vector in its
+    own last kernel; any other part writes into a scratch row that one more kernel scales and
+    adds."""
 
     def __init__(self, spec: LayerSpec, ctx: BuildContext, position: Part | None) -> None:
         super().__init__(ctx)
@@ -33,18 +40,27 @@ class PreNormBlock(Block):
             "mixer_norm", build_part("norm", spec.mixer_norm.kind, spec.mixer_norm, ctx))
         self.mixer = self.add_child(
             "mixer", build_part("mixer", spec.mixer.kind, spec.mixer, ctx, position))
-        self.feed_forward_norm = self.add_child(
+        # a layer without a feed-forward has no second norm either
+        self.feed_forward_norm = None if spec.feed_forward.kind == "none" else self.add_child(
             "feed_forward_norm",
             build_part("norm", spec.feed_forward_norm.kind, spec.feed_forward_norm, ctx))
         self.feed_forward = self.add_child(
             "feed_forward",
             build_part("feed_forward", spec.feed_forward.kind, spec.feed_forward, ctx))
         self.width = int(spec.mixer_norm.width)  # type: ignore[arg-type]
+        self.mixer_scale = self.feed_forward_scale = None
+        if spec.layer_scale:
+            self.mixer_scale = self.add_param("mixer_scale", (self.width,), "vector")
+            if spec.feed_forward.kind != "none":
+                self.feed_forward_scale = self.add_param("feed_forward_scale", (self.width,),
+                                                         "vector")
 
     def native_run(self, workspace: Workspace):  # noqa: ANN201
         """``(attention part, feed-forward part)`` for the C++ host code when both halves of
         this layer can run there (fusable norms, parts that know how to pack themselves),
         else ``None``; see ``kernels/native.py``."""
+        if self.mixer_scale is not None:
+            return None
         if not (_plain_norm(self.mixer_norm) and _plain_norm(self.feed_forward_norm)
                 and hasattr(self.mixer, "native_part")
                 and hasattr(self.feed_forward, "native_part")):
@@ -56,18 +72,52 @@ class PreNormBlock(Block):
     def forward(self, residual: torch.Tensor, step: StepContext, cache: LayerCache) -> None:
         n = step.num_rows
         hidden = step.workspace.buffer("block.normed", self.width, self.ctx.dtype)
+        if self.mixer_scale is not None:
+            self._forward_scaled(hidden, residual, step, cache)
+            return
         # a part that can apply the norm itself gets the residual and the norm part
         if hasattr(self.mixer, "forward_normed") and _plain_norm(self.mixer_norm):
             self.mixer.forward_normed(self.mixer_norm, residual, step, cache)  # type: ignore
         else:
             self.mixer_norm.forward(residual, hidden, count=n)  # type: ignore[attr-defined]
             self.mixer.forward(hidden, residual, step, cache)  # type: ignore[attr-defined]
+        if self.feed_forward_norm is None:
+            return
         if hasattr(self.feed_forward, "forward_normed") and _plain_norm(self.feed_forward_norm):
             self.feed_forward.forward_normed(  # type: ignore[attr-defined]
                 self.feed_forward_norm, residual, step)
         else:
             self.feed_forward_norm.forward(residual, hidden, count=n)  # type: ignore
             self.feed_forward.forward(hidden, residual, step)  # type: ignore[attr-defined]
+
+
+    def _forward_scaled(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext,
+                        cache: LayerCache) -> None:
+        n = step.num_rows
+        self.mixer_norm.forward(residual, hidden, count=n)  # type: ignore[attr-defined]
+        if hasattr(self.mixer, "forward_scaled"):
+            self.mixer.forward_scaled(hidden, residual, step, cache,  # type: ignore
+                                      self.mixer_scale)
+        else:
+            branch = self._empty_branch(step)
+            self.mixer.forward(hidden, branch, step, cache)  # type: ignore[attr-defined]
+            ops.scale_add(branch, self.mixer_scale, residual, rows=n)
+        if self.feed_forward_scale is None or self.feed_forward_norm is None:
+            return
+        self.feed_forward_norm.forward(residual, hidden, count=n)  # type: ignore
+        if hasattr(self.feed_forward, "forward_scaled"):
+            self.feed_forward.forward_scaled(hidden, residual, step,  # type: ignore
+                                             self.feed_forward_scale)
+        else:
+            branch = self._empty_branch(step)
+            self.feed_forward.forward(hidden, branch, step)  # type: ignore[attr-defined]
+            ops.scale_add(branch, self.feed_forward_scale, residual, rows=n)
+
+    def _empty_branch(self, step: StepContext) -> torch.Tensor:
+        """A zeroed fp32 scratch row per row of the step (parts add into what they get)."""
+        branch = step.workspace.buffer("block.branch", self.width, torch.float32)
+        branch[:step.num_rows].zero_()
+        return branch
 
 
 @register_part("block", "parallel")
@@ -96,7 +146,7 @@ class ParallelBlock(Block):
         self.feed_forward.forward(hidden, residual, step)  # type: ignore[attr-defined]
 
 
-def _plain_norm(norm: Part) -> bool:
+def _plain_norm(norm: Part | None) -> bool:
     """Whether ``norm`` declares itself a LayerNorm that a fused kernel can apply from its
     (weight, bias, eps); see ``parts/norm.py``."""
     return bool(getattr(norm, "fusable_layer_norm", False))

@@ -1,5 +1,5 @@
 """Mixers that carry a fixed-size state per request instead of cached keys: a Mamba-2
-state-space layer and an mLSTM matrix memory. The state lives in float32 in the request's
+state-space layer, an mLSTM matrix memory and a gated linear attention. The state lives in float32 in the request's
 slot of the cache storage's state tensor, starts at zero, and is carried through whatever
 rows a step brings: ``csrc/recurrent.cu``."""
 
@@ -13,7 +13,7 @@ from ayaka_b200.parts.context import LayerCache, StepContext
 from ayaka_b200.parts.mixer import Mixer
 from ayaka_b200.parts.spec import PartSpec
 
-__all__ = ["MLSTM", "Mamba2"]
+__all__ = ["MLSTM", "GatedLinearAttention", "Mamba2"]
 
 
 @register_part("mixer", "mamba2")
@@ -154,3 +154,81 @@ class MLSTM(Mixer):
         ops.rms_norm(answer, self.norm_weight, self.eps, gated, groups=heads, count=n,
                      gate=proj[:, gate_at:gate_at + self.inner], gate_mode="sigmoid_after")
         ops.linear(gated, self.out_weight, None, residual, residual=True, rows=n)
+
+
+@register_part("mixer", "gated_linear_attention")
+class GatedLinearAttention(Mixer):
+    """Linear attention with a learned decay per key channel.
+
+    One fused projection gives ``q`` (times ``dim^-1/2``), ``k`` (``heads x dim``), ``v``
+    (``heads x columns``) and an output gate (``heads x columns``); a low-rank pair of
+    projections gives the raw decays ``z = W_up (W_down h) + b`` (``heads x dim``). Per head
+    ``alpha = sigmoid(z)^(1/tau)``, ``S <- diag(alpha) S + k v^T``, ``out = S^T q``; each head's
+    ``out`` is normalised by its root mean square with one weight of ``columns`` entries that
+    all heads share; the joined heads are multiplied by ``silu(gate)`` and projected back.
+    Decays, their logarithms and the state are float32.
+
+    State of a request: ``S`` per head, ``[heads][columns][dim]``.
+
+    Spec parameters: ``width``, ``num_heads``, ``dim``, ``columns``, ``tau``, ``decay_rank``,
+    ``eps``.
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext, position: Part | None = None) -> None:
+        super().__init__(ctx)
+        self.width = int(spec.width)  # type: ignore[arg-type]
+        self.num_heads = heads = int(spec.num_heads)  # type: ignore[arg-type]
+        self.dim = int(spec.dim)  # type: ignore[arg-type]
+        self.columns = int(spec.columns)  # type: ignore[arg-type]
+        self.tau = float(spec.tau)  # type: ignore[arg-type]
+        self.decay_rank = int(spec.decay_rank)  # type: ignore[arg-type]
+        self.eps = float(spec.eps)  # type: ignore[arg-type]
+        if not 1 <= self.dim <= 512 or self.columns < 1 or heads < 1 or self.decay_rank < 1 \
+                or not self.tau > 0:
+            raise ValueError("gated linear attention takes dim in [1, 512], columns, heads and "
+                             "decay_rank >= 1 and a positive tau")
+        self.qk = heads * self.dim
+        self.inner = heads * self.columns
+        # q, k, v, output gate: one product
+        self.proj_weight = self.add_param("proj.weight", (2 * self.qk + 2 * self.inner,
+                                                          self.width), "matrix")
+        self.decay_down = self.add_param("decay_down.weight", (self.decay_rank, self.width),
+                                         "matrix")
+        self.decay_up = self.add_param("decay_up.weight", (self.qk, self.decay_rank), "matrix")
+        self.decay_bias = self.add_param("decay_up.bias", (self.qk,), "vector")
+        self.norm_weight = self.add_param("norm.weight", (self.columns,), "vector")
+        self.out_weight = self.add_param("out.weight", (self.width, self.inner), "matrix")
+
+    def state_need(self) -> StateNeed:
+        return StateNeed((self.num_heads * self.dim * self.columns,))
+
+    def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext,
+                cache: LayerCache) -> None:
+        self._run(hidden, residual, step, cache, accumulate=True)
+
+    def forward_into(self, hidden: torch.Tensor, out: torch.Tensor, step: StepContext,
+                     cache: LayerCache) -> None:
+        """The same, written into ``out`` (fp32 ``[N, width]``) instead of added to it."""
+        self._run(hidden, out, step, cache, accumulate=False)
+
+    def _run(self, hidden: torch.Tensor, out: torch.Tensor, step: StepContext,
+             cache: LayerCache, accumulate: bool) -> None:
+        n, work, heads = step.num_rows, step.workspace, self.num_heads
+        state = cache.state
+        assert state is not None
+        proj = work.buffer("gla.proj", self.proj_weight.shape[0], torch.float32)
+        low = work.buffer("gla.low", self.decay_rank, self.ctx.dtype)
+        decay = work.buffer("gla.decay", self.qk, torch.float32)
+        answer = work.buffer("gla.answer", self.inner, torch.float32)
+        gated = work.buffer("gla.gated", self.inner, self.ctx.dtype)
+        ops.linear(hidden, self.proj_weight, None, proj, rows=n)
+        ops.linear(hidden, self.decay_down, None, low, rows=n)
+        ops.linear(low, self.decay_up, self.decay_bias, decay, rows=n)
+        ops.gla_scan(proj, decay, state, answer, row_start=step.row_start,
+                     state_slot=step.state_slot, requests=step.num_requests, heads=heads,
+                     dim=self.dim, columns=self.columns, k_offset=self.qk, v_offset=2 * self.qk,
+                     tau=self.tau, q_scale=self.dim ** -0.5)
+        # a head is a group of the norm; the weight's `columns` entries repeat for every head
+        ops.rms_norm(answer, self.norm_weight, self.eps, gated, groups=heads, count=n,
+                     gate=proj[:, 2 * self.qk + self.inner:], gate_mode="silu_after")
+        ops.linear(gated, self.out_weight, None, out, residual=accumulate, rows=n)

@@ -64,6 +64,9 @@ class LayerSpec:
     feed_forward: PartSpec
     mixer_norm: PartSpec
     feed_forward_norm: PartSpec
+    #: each half's result is multiplied element by element by a learned vector of the model's
+    #: width before it joins the residual stream (blocks that know of it declare the vectors)
+    layer_scale: bool = False
 
 
 @dataclass(frozen=True, slots=True)
