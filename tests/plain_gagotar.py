@@ -90,6 +90,38 @@ def chunk_mask(T: int, size: int) -> torch.Tensor:
     return (t[None, :] <= t[:, None]) & ((t[None, :] // size) == (t[:, None] // size))
 
 
+def mixed_head_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                         talk: torch.Tensor, temp: torch.Tensor, scale: float,
+                         size: int) -> torch.Tensor:
+    """q [T, H, dim], k [T, G, dim], v [T, G, vdim] -> [T, H, vdim]. Head a's raw score is
+    scale * temp[a] * (q_a . k_(a // (H/G))); every (t, s) pair's H scores are mixed by
+    ``talk`` (score_h = sum_a talk[h, a] raw_a); softmax over the keys of t's own block of
+    ``size`` positions up to t; head h sums the values of its own key/value head."""
+    T, H, _ = q.shape
+    per = H // k.shape[1]
+    raw = torch.stack([q[:, a, :] @ k[:, a // per, :].T for a in range(H)])  # [H, T, T]
+    raw = raw * scale * temp[:, None, None]
+    score = torch.einsum("ha,ats->hts", talk, raw)
+    score = score.masked_fill(~chunk_mask(T, size)[None], float("-inf"))
+    weight = torch.softmax(score, dim=-1)
+    return torch.stack([weight[h] @ v[:, h // per, :] for h in range(H)], dim=1)
+
+
+def decayed_memory(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
+                   tau: float, state: torch.Tensor | None = None
+                   ) -> tuple[torch.Tensor, torch.Tensor]:
+    """q, k, z [T, H, dim], v [T, H, vdim]. Token by token S <- diag(sigmoid(z)^(1/tau)) S +
+    k v^T and out = S^T q; returns out [T, H, vdim] and the last S [H, dim, vdim]."""
+    T, H, dim = q.shape
+    decay = torch.sigmoid(z) ** (1.0 / tau)
+    S = torch.zeros(H, dim, v.shape[2], dtype=q.dtype) if state is None else state.clone()
+    out = torch.empty(T, H, v.shape[2], dtype=q.dtype)
+    for t in range(T):
+        S = decay[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        out[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    return out, S
+
+
 # ---------------------------------------------------------------------------------------------
 # the two sides of the mixer
 
@@ -108,14 +140,7 @@ def softmax_side(h: torch.Tensor, w: dict, m: dict, eps: float) -> torch.Tensor:
     rot = m["rot"]
     freq = scaled_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
     q, k = rotate_halves(q, positions, freq), rotate_halves(k, positions, freq)
-    per = H // G
-    score = torch.stack([q[:, a, :] @ k[:, a // per, :].T for a in range(H)])  # [H, T, T]
-    score = score * m["scale"] * w["temp"][:, None, None]
-    score = torch.einsum("ab,bts->ats", w["talk"], score)  # heads' scores mixed before softmax
-    visible = chunk_mask(T, m["mask"]["size"])
-    score = score.masked_fill(~visible[None], float("-inf"))
-    weight = torch.softmax(score, dim=-1)
-    out = torch.stack([weight[a] @ v[:, a // per, :] for a in range(H)], dim=1)  # [T, H, vdim]
+    out = mixed_head_attention(q, k, v, w["talk"], w["temp"], m["scale"], m["mask"]["size"])
     gate = torch.sigmoid(linear(h, w["g"]))  # [T, H]: one number per head
     out = out * gate[:, :, None]
     return linear(out.reshape(T, H * vdim), w["o"])
@@ -131,12 +156,7 @@ def linear_side(h: torch.Tensor, w: dict, m: dict, eps: float,
     k = linear(h, w["k"]).reshape(T, H, dim)
     v = linear(h, w["v"]).reshape(T, H, vdim)
     z = linear(linear(h, w["a1"]), w["a2"], w["a2.b"]).reshape(T, H, dim)
-    decay = torch.sigmoid(z) ** (1.0 / tau)
-    S = torch.zeros(H, dim, vdim, dtype=h.dtype) if state is None else state.clone()
-    out = torch.empty(T, H, vdim, dtype=h.dtype)
-    for t in range(T):
-        S = decay[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        out[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    out, S = decayed_memory(q, k, v, z, tau, state)
     out = rms(out, eps) * w["norm"]  # every head over its own vdim entries, one shared weight
     out = out.reshape(T, H * vdim) * silu(linear(h, w["g"]))
     return linear(out, w["o"]), S
@@ -220,3 +240,13 @@ def logits(state: dict, config: dict, tokens: torch.Tensor) -> torch.Tensor:
 
 def cast_state(state: dict, dtype: torch.dtype) -> dict:
     return {name: t.to(dtype) if t.is_floating_point() else t for name, t in state.items()}
+
+
+def greedy_generate(state: dict, config: dict, prompt: list[int], count: int) -> list[int]:
+    """``count`` tokens, each the largest logit (smallest id on ties) of the whole sequence
+    so far run from scratch."""
+    tokens = list(prompt)
+    for _ in range(count):
+        last = logits(state, config, torch.tensor(tokens))[-1]
+        tokens.append(int(torch.argmax(last)))
+    return tokens[len(prompt):]
