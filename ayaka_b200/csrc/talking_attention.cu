@@ -13,11 +13,12 @@
 // prepare (one launch per layer): from a row of the fused projection (fp32): the norm of the
 // whole query projection and of the whole key projection by their root mean square (one
 // mean over all heads' entries, a weight per entry; a bias of the projection is added first:
-// `bias` follows the projection's columns, queries, keys, values), the rotation of the first `rot_dims`
-// entries of every head, the mixed queries m (compute type), and the row's key and value
-// into its cache slot.
-// attention: one CTA per (row, head); fp32 scores, softmax and sums; the result times
-// sigmoid(gate[h]) when a gate is given.
+// `bias` follows the projection's columns, queries, keys, values), the rotation of the first
+// `rot_dims` entries of every head, the mixed queries m (compute type), and the row's key and
+// value into its cache slot.
+// attention: fp32 scores, softmax and sums; the result times sigmoid(gate[h]) when a gate is
+// given. float32: one CTA per (row, head) on the CUDA cores; bfloat16: the tensor-core kernel
+// further down where the sizes allow.
 #include "rope.cuh"
 
 namespace ayk {
@@ -28,8 +29,8 @@ constexpr int ATT_THREADS = 128;
 template <typename T>
 __global__ void __launch_bounds__(TALK_THREADS)
 talking_prepare_kernel(const float* __restrict__ proj, int ld_proj, int k_off, int v_off,
-                       const float* __restrict__ bias, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
-                       float eps, const int* __restrict__ positions,
+                       const float* __restrict__ bias, const float* __restrict__ q_weight,
+                       const float* __restrict__ k_weight, float eps, const int* __restrict__ positions,
                        const double* __restrict__ freq, int rot_dims, int layout,
                        const float* __restrict__ talk, const float* __restrict__ temp,
                        float scale, const int* __restrict__ slot_mapping,
@@ -178,6 +179,247 @@ talking_attention_kernel(const T* __restrict__ qmix, int ld_qmix, const T* __res
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same attention on the warp-level tensor cores (bfloat16). A CTA takes `window_rows`
+// consecutive rows of the step (16 for steps with prompt portions, 1 for steps of single
+// rows, where a row's keys are its own) and eight heads, a warp per head. The rows of a
+// window that belong to one request and one block of positions form a *segment*: they see
+// the same keys, up to each row's own position. Per segment the keys come in tiles of 32:
+// the CTA copies a tile's keys (all key heads side by side, as the mixed queries want them)
+// and values into shared memory once, and every warp computes its head's scores
+// (mma.sync m16n8k16, fp32 accumulators, the mixed queries held in registers), an online
+// softmax in fp32, and the weighted sum of its key/value head's values. The weights enter
+// that product as two bfloat16 terms, w = hi + lo, so that they carry 16 bits of mantissa
+// instead of 8. Keys past the segment's last position are zero in shared memory.
+constexpr int MMA_HEADS = 8;
+constexpr int MMA_KEYS = 32;
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int KSTEPS, int VT>  // G * dim <= 16 KSTEPS, vdim <= 8 VT
+__global__ void __launch_bounds__(MMA_HEADS * 32)
+talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix,
+                             const __nv_bfloat16* __restrict__ k_pages,
+                             const __nv_bfloat16* __restrict__ v_pages,
+                             const int* __restrict__ block_table, int ld_table,
+                             const int* __restrict__ request_of_row,
+                             const int* __restrict__ positions, const float* __restrict__ gate,
+                             int ld_gate, __nv_bfloat16* __restrict__ out, int ld_out, int rows,
+                             int H, int G, int dim, int vdim, int page_size, int chunk,
+                             int window_rows) {
+  extern __shared__ __align__(16) unsigned char mma_smem[];
+  __shared__ int req_s[16], pos_s[16];
+  using bf16 = __nv_bfloat16;
+  const int kn = G * dim, vn = G * vdim;
+  const int ldk = kn + 8, ldv = vn + 8;  // rows padded: a fragment's rows in different banks
+  bf16* Ks = reinterpret_cast<bf16*>(mma_smem);
+  bf16* Vs = Ks + MMA_KEYS * ldk;
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * window_rows, nrows = min(window_rows, rows - row0);
+  const int h = blockIdx.y * MMA_HEADS + warp;
+  const bool active = h < H;
+  if (tid < 16) {
+    req_s[tid] = tid < nrows ? request_of_row[row0 + tid] : -1;
+    pos_s[tid] = tid < nrows ? positions[row0 + tid] : 0;
+  }
+  pdl_wait_for(qmix, k_pages, v_pages, gate);
+  __syncthreads();
+  // the head's mixed queries as A fragments: rows g and g + 8, k-step by k-step
+  uint32_t qa[KSTEPS][4];
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = g + (i & 1) * 8, c = ks * 16 + 2 * t + (i >> 1) * 8;
+      qa[ks][i] = (active && r < nrows && c < kn)
+                      ? *reinterpret_cast<const uint32_t*>(
+                            qmix + (size_t)(row0 + r) * ld_qmix + (size_t)h * kn + c)
+                      : 0u;
+    }
+  }
+  float o[VT][4];
+#pragma unroll
+  for (int v = 0; v < VT; ++v)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[v][i] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int kvh = active ? h / (H / G) : 0;
+  const bool wide = (dim % 8 == 0) && (vdim % 8 == 0);  // 16-byte copies
+
+  int first = 0;
+  while (first < nrows) {
+    const int b = req_s[first];
+    int last = first;
+    if (b >= 0) {
+      const int block = chunk > 0 ? pos_s[first] / chunk : 0;
+      while (last + 1 < nrows && req_s[last + 1] == b &&
+             (chunk > 0 ? pos_s[last + 1] / chunk : 0) == block &&
+             pos_s[last + 1] == pos_s[last] + 1) {
+        ++last;
+      }
+    }
+    if (b >= 0) {
+      const int c0 = chunk > 0 ? pos_s[first] - pos_s[first] % chunk : 0;
+      const int p_last = pos_s[last];
+      const int* table = block_table + (size_t)b * ld_table;
+      for (int k0 = c0; k0 <= p_last; k0 += MMA_KEYS) {
+        // the tile's keys and values into shared memory, zeros past the last position
+        if (wide) {
+          const int kc = kn / 8, vc = vn / 8;
+          for (int idx = tid; idx < MMA_KEYS * (kc + vc); idx += MMA_HEADS * 32) {
+            const int j = idx / (kc + vc), c = idx % (kc + vc);
+            const int at = k0 + j;
+            uint4 value = make_uint4(0u, 0u, 0u, 0u);
+            const bool key = c < kc;
+            const int e = (key ? c : c - kc) * 8;  // entry among the token's kn (vn)
+            if (at <= p_last) {
+              const int page = table[at / page_size], s = at % page_size;
+              const int width = key ? dim : vdim, head = e / width, d = e % width;
+              const bf16* src = (key ? k_pages : v_pages) +
+                                (((size_t)page * G + head) * page_size + s) * width + d;
+              value = *reinterpret_cast<const uint4*>(src);
+            }
+            *reinterpret_cast<uint4*>((key ? Ks + j * ldk : Vs + j * ldv) + e) = value;
+          }
+        } else {
+          for (int idx = tid; idx < MMA_KEYS * (kn + vn); idx += MMA_HEADS * 32) {
+            const int j = idx / (kn + vn), c = idx % (kn + vn);
+            const int at = k0 + j;
+            const bool key = c < kn;
+            const int e = key ? c : c - kn;
+            bf16 value = __float2bfloat16_rn(0.f);
+            if (at <= p_last) {
+              const int page = table[at / page_size], s = at % page_size;
+              const int width = key ? dim : vdim, head = e / width, d = e % width;
+              value = (key ? k_pages : v_pages)[(((size_t)page * G + head) * page_size + s) *
+                                                    width + d];
+            }
+            (key ? Ks + j * ldk : Vs + j * ldv)[e] = value;
+          }
+        }
+        __syncthreads();
+        if (active) {
+          float sc[MMA_KEYS / 8][4];
+#pragma unroll
+          for (int n = 0; n < MMA_KEYS / 8; ++n) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[n][i] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+              if (ks * 16 < kn) {
+                const bf16* kb = Ks + (n * 8 + g) * ldk + ks * 16 + 2 * t;
+                mma_bf16(sc[n], qa[ks], *reinterpret_cast<const uint32_t*>(kb),
+                         *reinterpret_cast<const uint32_t*>(kb + 8));
+              }
+            }
+          }
+          // rows g (i = 0, 1) and g + 8 (i = 2, 3); key of column n * 8 + 2 t + (i & 1)
+          float alpha[2];
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int r = g + 8 * half;
+            const bool mine = r >= first && r <= last;
+            const int reach = mine ? pos_s[r] : -1;
+            float best = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < MMA_KEYS / 8; ++n) {
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const int at = k0 + n * 8 + 2 * t + i;
+                float& v = sc[n][2 * half + i];
+                v = at <= reach ? v : -INFINITY;
+                best = fmaxf(best, v);
+              }
+            }
+            best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, 1));
+            best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, 2));
+            const float m_new = fmaxf(m_run[half], best);
+            alpha[half] = m_new == -INFINITY ? 1.f : expf(m_run[half] - m_new);
+            float sum = 0.f;
+#pragma unroll
+            for (int n = 0; n < MMA_KEYS / 8; ++n) {
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                float& v = sc[n][2 * half + i];
+                v = m_new == -INFINITY ? 0.f : expf(v - m_new);
+                sum += v;
+              }
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            l_run[half] = l_run[half] * alpha[half] + sum;
+            m_run[half] = m_new;
+          }
+#pragma unroll
+          for (int v = 0; v < VT; ++v) {
+            o[v][0] *= alpha[0];
+            o[v][1] *= alpha[0];
+            o[v][2] *= alpha[1];
+            o[v][3] *= alpha[1];
+          }
+#pragma unroll
+          for (int kk = 0; kk < MMA_KEYS / 16; ++kk) {
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              // a0: row g, keys 2t..; a1: row g + 8; a2, a3: the same rows, keys + 8
+              const float w0 = sc[2 * kk + (i >> 1)][2 * (i & 1)];
+              const float w1 = sc[2 * kk + (i >> 1)][2 * (i & 1) + 1];
+              const float h0 = __bfloat162float(__float2bfloat16_rn(w0));
+              const float h1 = __bfloat162float(__float2bfloat16_rn(w1));
+              hi[i] = pack_bf16(h0, h1);
+              lo[i] = pack_bf16(w0 - h0, w1 - h1);
+            }
+#pragma unroll
+            for (int v = 0; v < VT; ++v) {
+              if (v * 8 < vdim) {
+                const int col = kvh * vdim + v * 8 + g;
+                const unsigned short* vb =
+                    reinterpret_cast<const unsigned short*>(Vs) + (kk * 16 + 2 * t) * ldv + col;
+                const uint32_t b0 = (uint32_t)vb[0] | ((uint32_t)vb[ldv] << 16);
+                const uint32_t b1 = (uint32_t)vb[8 * ldv] | ((uint32_t)vb[9 * ldv] << 16);
+                mma_bf16(o[v], hi, b0, b1);
+                mma_bf16(o[v], lo, b0, b1);
+              }
+            }
+          }
+        }
+        __syncthreads();  // the tile is overwritten at the next turn
+      }
+    }
+    first = last + 1;
+  }
+  if (!active) return;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = g + 8 * half;
+    if (r >= nrows) continue;
+    float factor = l_run[half] > 0.f ? 1.f / l_run[half] : 0.f;
+    if (gate != nullptr) factor /= 1.f + expf(-gate[(size_t)(row0 + r) * ld_gate + h]);
+    bf16* dst = out + (size_t)(row0 + r) * ld_out + (size_t)h * vdim;
+#pragma unroll
+    for (int v = 0; v < VT; ++v) {
+      const int c = v * 8 + 2 * t;
+      if (c < vdim) {  // (vdim is a multiple of 8 here: both columns are inside)
+        *reinterpret_cast<uint32_t*>(dst + c) =
+            pack_bf16(o[v][2 * half] * factor, o[v][2 * half + 1] * factor);
+      }
+    }
+  }
+}
+
 template <typename K> inline void allow_large_smem(K kernel) {
   cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
 }
@@ -257,13 +499,16 @@ AYK_API int ayk_talking_prepare(const float* proj, int ld_proj, int k_off, int v
   return AYK_BAD_ARGUMENT;
 }
 
-// `reach`: the most keys any row of the launch sees (bounds the shared memory).
+// `reach`: the most keys any row of the launch sees (bounds the shared memory of the CUDA-core
+// kernel). `window_rows`: rows of the step per CTA of the tensor-core kernel, which serves
+// bfloat16 when the sizes allow (1: a step of single rows; 16: prompt portions; 0: never).
 AYK_API int ayk_talking_attention(const void* qmix, int ld_qmix, const void* k_pages,
                                   const void* v_pages, const int* block_table, int ld_table,
                                   const int* request_of_row, const int* positions,
                                   const float* gate, int ld_gate, void* out, int ld_out, int rows,
                                   int H, int G, int dim, int vdim, int page_size, int chunk,
-                                  int window, int reach, int type, void* stream) {
+                                  int window, int reach, int window_rows, int type,
+                                  void* stream) {
   using namespace ayk;
   if (rows == 0) return AYK_OK;
   if (rows < 0 || H < 1 || G < 1 || H % G || dim < 1 || vdim < 1 || qmix == nullptr ||
@@ -274,6 +519,30 @@ AYK_API int ayk_talking_attention(const void* qmix, int ld_qmix, const void* k_p
     return AYK_BAD_ARGUMENT;
   }
   cudaStream_t s = (cudaStream_t)stream;
+  const int kn = G * dim;
+  const size_t mma_smem = (size_t)MMA_KEYS * (kn + 8 + G * vdim + 8) * sizeof(__nv_bfloat16);
+  if (type == 1 && window == 0 && window_rows >= 1 && window_rows <= 16 && kn % 16 == 0 &&
+      kn <= 256 && vdim % 8 == 0 && vdim <= 128 && mma_smem <= 160 * 1024 &&
+      ld_qmix % 2 == 0 && ld_out % 2 == 0 && ((uintptr_t)qmix | (uintptr_t)out) % 4 == 0 &&
+      ((uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0) {
+    const dim3 grid((rows + window_rows - 1) / window_rows, (H + MMA_HEADS - 1) / MMA_HEADS);
+#define AYK_TALK_MMA(KS, VT)                                                                   \
+  {                                                                                            \
+    static const bool allowed = (allow_large_smem(talking_attention_mma_kernel<KS, VT>), true); \
+    (void)allowed;                                                                             \
+    return launch_kernel(talking_attention_mma_kernel<KS, VT>, grid, dim3(MMA_HEADS * 32),     \
+                         mma_smem, s, 1, (const __nv_bfloat16*)qmix, ld_qmix,                  \
+                         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,         \
+                         block_table, ld_table, request_of_row, positions, gate, ld_gate,      \
+                         (__nv_bfloat16*)out, ld_out, rows, H, G, dim, vdim, page_size, chunk, \
+                         window_rows);                                                         \
+  }
+    if (kn <= 128 && vdim <= 64) AYK_TALK_MMA(8, 8);
+    if (kn <= 128) AYK_TALK_MMA(8, 16);
+    if (vdim <= 64) AYK_TALK_MMA(16, 8);
+    AYK_TALK_MMA(16, 16);
+#undef AYK_TALK_MMA
+  }
   if (type == 0) {
     return talking_attention<float>(qmix, ld_qmix, k_pages, v_pages, block_table, ld_table,
                                     request_of_row, positions, gate, ld_gate, out, ld_out, rows,

@@ -1215,14 +1215,18 @@ def talking_attention(qmix: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
                       block_table: torch.Tensor, request_of_row: torch.Tensor,
                       positions: torch.Tensor, out: torch.Tensor, *, heads: int, chunk: int = 0,
                       window: int = 0, reach: int, gate: torch.Tensor | None = None,
-                      rows: int | None = None) -> None:
+                      rows: int | None = None, single_rows: bool = False,
+                      tensor_cores: bool = True) -> None:
     """Softmax attention of mixed queries (see :func:`talking_prepare`; every factor is in
     them) over paged keys and values. The row of request ``request_of_row[i]`` at
     ``positions[i]`` sees the keys from the start of its block of ``chunk`` positions
     (``chunk`` 0: from 0), and no further back than ``window`` (0: no limit), up to itself;
     head ``h`` sums the values of key/value head ``h // (heads / kv_heads)``; with ``gate``
     (float32 ``[N, heads]``) its result is multiplied by ``sigmoid(gate[:, h])``. ``reach``
-    bounds the keys any row sees. The step's own keys must already be stored."""
+    bounds the keys any row sees. The step's own keys must already be stored. bfloat16 runs
+    on the warp-level tensor cores where the sizes allow (``tensor_cores=False``: never), with
+    a CTA per row when ``single_rows`` says that every request brings one row, else per 16
+    rows; float32 on the CUDA cores."""
     op = "talking_attention"
     if _left_out and op in _left_out:
         return
@@ -1251,7 +1255,9 @@ def talking_attention(qmix: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
         c_int(block_table.stride(0)), _ptr(request_of_row), _ptr(positions), _ptr(gate),
         c_int(0 if gate is None else gate.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(n),
         c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(page_size), c_int(chunk),
-        c_int(window), c_int(max(1, reach)), c_int(_TYPE[qmix.dtype]), _stream())
+        c_int(window), c_int(max(1, reach)),
+        c_int(0 if not tensor_cores else (1 if single_rows else 16)), c_int(_TYPE[qmix.dtype]),
+        _stream())
     check(status, op)
 
 

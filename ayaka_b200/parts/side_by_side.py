@@ -184,5 +184,6 @@ class TalkingAttention(Mixer):
         ops.talking_attention(
             qmix, cache.k_pages, cache.v_pages, group.block_table, step.request_of_row,
             step.positions, attended, heads=heads, chunk=self.chunk, window=self.window,
-            reach=reach, gate=proj[:, self.qkv_width:] if self.head_gate else None, rows=n)
+            reach=reach, gate=proj[:, self.qkv_width:] if self.head_gate else None, rows=n,
+            single_rows=step.decode_only)
         ops.linear(attended, self.out_weight, None, out, residual=accumulate, rows=n)

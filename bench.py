@@ -20,7 +20,8 @@ class costs inside the step (the step replayed as a CUDA graph with and without 
 and its fraction of the roofline that bounds it. ``workloads`` holds the two serving
 workloads of BASELINE.json's other configurations (see :func:`workload_run`);
 ``--workload small|large`` runs one of them alone and prints a line of its own;
-``--design mapuvik`` runs that design beside GPT-2 of equal size (``bench_design.py``).
+``--design mapuvik`` runs that design beside GPT-2 of equal size, ``--design gagotar`` that
+design beside Mapuvik and GPT-2 (``bench_design.py``).
 """
 
 from __future__ import annotations
@@ -517,10 +518,11 @@ def main() -> int:
                         help="instead of the headline run: one of the two serving workloads "
                              "(GPT-2 small with 64 ragged requests; GPT-2 large with prompt "
                              "portions beside 32 decoding requests)")
-    parser.add_argument("--design", choices=("mapuvik",),
-                        help="instead of the headline run: the named design beside GPT-2 of "
-                             "equal size, prompt step and decode step with per-kernel times "
-                             "(bench_design.py); --sizes picks among 1024,2048")
+    parser.add_argument("--design", choices=("mapuvik", "gagotar"),
+                        help="instead of the headline run: the named design beside GPT-2 (and, "
+                             "for gagotar, Mapuvik) of equal size, prompt step and decode step "
+                             "with per-kernel times (bench_design.py); --sizes picks among "
+                             "1024,2048")
     parser.add_argument("--sizes", default=None, help="with --design: widths to run")
     args = parser.parse_args()
     if args.gpus != 1:
@@ -539,7 +541,7 @@ def main() -> int:
     if args.design:
         import bench_design
 
-        print(json.dumps(bench_design.run(args.sizes)))
+        print(json.dumps(bench_design.run(args.sizes, args.design)))
         return 0
     warmup = max(args.warmup, 3)
     steps = max(1, min(args.steps, XL["n_positions"] - PROMPT - 2 - warmup))

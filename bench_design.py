@@ -1,6 +1,7 @@
-"""``bench.py --design mapuvik``: prefill and decode throughput of Mapuvik at sizes that
-resemble a real model's layers, beside GPT-2 of the same width, heads, feed-forward and
-number of layers, on one B200 with random bf16 weights.
+"""``bench.py --design mapuvik`` / ``--design gagotar``: prefill and decode throughput of the
+design at sizes that resemble a real model's layers, beside GPT-2 of the same width, heads,
+feed-forward and number of layers (Gagotar also beside Mapuvik, the design whose kernels are
+closest to its own), on one B200 with random bf16 weights.
 
 For each size and model: one prompt step of 2,048 tokens (two prompts of 1,024) and one decode
 step of 8 requests at context 1,025, each timed on the device as a CUDA-graph replay of the
@@ -38,6 +39,28 @@ def mapuvik_config(width: int, heads: int, ff: int, repeats: int, vocab: int) ->
     layers = [{**kind, "mlp": mlp} for _ in range(repeats) for kind in (latent, mamba, mlstm)]
     return {"architecture": "Mapuvik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
             "layers": layers}
+
+
+#: Gagotar at the bench's sizes: blocks of 384 positions (a prompt of 1,024 holds two and
+#: two thirds of one, and the decode step at context 1,025 sees 257 keys); experts of a
+#: quarter of the dense feed-forward's width, two of sixteen per row
+GAGOTAR_CHUNK, GAGOTAR_EXPERTS, GAGOTAR_TOP = 384, 16, 2
+
+
+def gagotar_config(width: int, heads: int, ff: int, layers: int, vocab: int) -> dict:
+    head = width // heads
+    left = {"heads": heads, "kv_heads": heads // 4, "dim": head, "vdim": head,
+            "scale": head ** -0.5, "mask": {"size": GAGOTAR_CHUNK},
+            "rot": {"base": 500000.0, "dims": head,
+                    "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    memory_heads = max(1, width // 256)
+    right = {"heads": memory_heads, "dim": 128, "vdim": width // memory_heads, "tau": 16.0,
+             "rank": 16}
+    mlp = {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0},
+           "router": {"experts": GAGOTAR_EXPERTS, "top": GAGOTAR_TOP}}
+    entry = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp}
+    return {"architecture": "Gagotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [entry for _ in range(layers)]}
 
 
 def gpt2_config(width: int, heads: int, ff: int, layers: int, vocab: int) -> dict:
@@ -100,6 +123,41 @@ def _class_work(config: dict, rows: int, keys_per_row: float, decode: bool,
         product(config["vocab_size"], d, 4, wanted)
         return work
     width = config["width"]
+    if config["architecture"] == "Gagotar":
+        for layer in config["layers"]:
+            a, r, mlp = layer["mixer"]["left"], layer["mixer"]["right"], layer["mlp"]
+            H, G, dim, vdim = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            chunk = a["mask"]["size"]
+            # keys a row sees: half a block on average in a prompt; in a decode step the
+            # place of the context's last position in its block
+            keys = (int(keys_per_row) - 1) % chunk + 1 if decode else \
+                sum(p % chunk + 1 for p in range(LENGTH)) / LENGTH
+            add("rms_norm", 0.0, 2 * rows * width * 6)
+            product(H * dim + G * dim + G * vdim + H, width, 4)
+            product(width, H * vdim, 4)
+            add("talking_prepare", 2.0 * rows * H * H * dim,
+                rows * ((H * dim + G * (dim + vdim)) * 4 + (H * G * dim + G * (dim + vdim)) * 2))
+            add("talking_attention", 2.0 * rows * keys * H * (dim + vdim + H),
+                rows * keys * G * (dim + vdim) * 2 / (1 if decode else chunk / 8)
+                + rows * H * (G * dim + vdim) * 2)
+            Hr, N, P = r["heads"], r["dim"], r["vdim"]
+            product(2 * Hr * N + 2 * Hr * P, width, 4)
+            product(r["rank"], width)
+            product(Hr * N, r["rank"], 4)
+            product(width, Hr * P, 4)
+            add("gla_scan", 6.0 * rows * Hr * N * P,
+                rows * (3 * Hr * N + 2 * Hr * P) * 4 + (2 * Hr * N * P * 4) * (
+                    rows if decode else 2))
+            add("rms_norm", 0.0, rows * Hr * P * 10)
+            add("norm_sum", 0.0, rows * width * 16)
+            E, top, f = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+            product(E, width, 4)
+            add("moe_route", 0.0, rows * (E + 2 * top) * 4)
+            add("moe_experts", 2.0 * rows * top * 3 * f * width,
+                min(E, rows * top) * 3 * f * width * 2 + rows * top * (width * 6 + f * 4))
+            add("moe_join", 0.0, rows * width * (4 * top + 8))
+        product(config["vocab"], width, 4, wanted)
+        return work
     for layer in config["layers"]:
         m = layer["mixer"]
         if layer["mlp"]:
@@ -227,7 +285,7 @@ def _measure(config: dict, peak: dict) -> dict:
             by_flops = work[name]["flops"] / seconds / tflops
             by_bytes = work[name]["bytes"] / seconds / gbs
             tensor = not decode and (name.startswith("linear") or "attention" in name
-                                     or name == "head_linear")
+                                     or name in ("head_linear", "moe_experts"))
             entry["frac"] = round(by_flops if tensor else by_bytes, 4)
             entry["of"] = "bf16_tflops" if tensor else "hbm_gbs"
         return found
@@ -271,7 +329,7 @@ def _measure(config: dict, peak: dict) -> dict:
     return out
 
 
-def run(sizes: str | None = None) -> dict:
+def run(sizes: str | None = None, design: str = "mapuvik") -> dict:
     from bench import peaks
 
     peak, source = peaks()
@@ -280,12 +338,15 @@ def run(sizes: str | None = None) -> dict:
     results = {}
     for name in picked:
         width, heads, ff, repeats = table[name]
-        results[name] = {
-            "layers": 3 * repeats, "width": width, "heads": heads, "ff": ff,
-            "mapuvik": _measure(mapuvik_config(width, heads, ff, repeats, 32000), peak),
-            "gpt2": _measure(gpt2_config(width, heads, ff, 3 * repeats, 32000), peak),
-        }
-    return {"metric": "Mapuvik beside GPT-2 of equal size: one 2,048-token prompt step and one "
+        results[name] = {"layers": 3 * repeats, "width": width, "heads": heads, "ff": ff}
+        if design == "gagotar":
+            results[name]["gagotar"] = _measure(
+                gagotar_config(width, heads, ff, 3 * repeats, 32000), peak)
+        results[name]["mapuvik"] = _measure(mapuvik_config(width, heads, ff, repeats, 32000),
+                                            peak)
+        results[name]["gpt2"] = _measure(gpt2_config(width, heads, ff, 3 * repeats, 32000), peak)
+    title = "Gagotar beside Mapuvik and GPT-2" if design == "gagotar" else "Mapuvik beside GPT-2"
+    return {"metric": f"{title} of equal size: one 2,048-token prompt step and one "
                       "decode step of 8 requests at context 1,025 (bf16, random weights)",
             "peaks": {**{k: peak[k] for k in ("hbm_gbs", "bf16_tflops")}, "source": source},
             "timing": "CUDA-graph replay of the model's forward, device time, best of 5 / 10",

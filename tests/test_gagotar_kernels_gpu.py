@@ -113,7 +113,8 @@ def _attention_case(dtype, *, H, G, dim, vdim, chunk, page, turned, lengths, cut
         ops.talking_attention(qmix, k_pages, v_pages, table.to(DEV),
                               torch.tensor(request_of_row, dtype=torch.int32, device=DEV), pos,
                               out, heads=H, chunk=chunk, reach=min(chunk, max(lengths)),
-                              gate=step_proj[:, q_w + k_w + v_w:q_w + k_w + v_w + H], rows=n)
+                              gate=step_proj[:, q_w + k_w + v_w:q_w + k_w + v_w + H], rows=n,
+                              single_rows=all(hi - lo == 1 for lo, hi in spans))
         torch.cuda.synchronize()
         got[rows_of] = out.double().cpu()
         second = rows_of
@@ -128,6 +129,14 @@ def _attention_case(dtype, *, H, G, dim, vdim, chunk, page, turned, lengths, cut
     dict(H=6, G=1, dim=12, vdim=40, chunk=64, page=16, turned=0, lengths=(150, 64, 65),
          cut=(63, 64, 0)),
     dict(H=1, G=1, dim=32, vdim=32, chunk=300, page=32, turned=32, lengths=(170,), cut=(100,)),
+    # sizes of every variant of the tensor-core kernel, more heads than a CTA takes, and
+    # steps of single rows (each request's last token alone)
+    dict(H=6, G=2, dim=80, vdim=104, chunk=48, page=16, turned=40, lengths=(100, 49, 7),
+         cut=(3, 48, 0)),
+    dict(H=12, G=4, dim=64, vdim=40, chunk=33, page=16, turned=64, lengths=(70, 34),
+         cut=(69, 33)),
+    dict(H=2, G=1, dim=64, vdim=72, chunk=16, page=8, turned=2, lengths=(40, 17, 16, 1),
+         cut=(39, 16, 15, 0)),
 ])
 def test_prepare_and_attention_over_scrambled_pages(dtype, case):
     got, want = _attention_case(dtype, normed=True, loud=False, seed=5, **case)
@@ -139,7 +148,8 @@ def test_a_loud_key_just_outside_the_block_is_not_seen(dtype):
     """No norm, so that loud rows stay loud: in every block the first key is loud and the
     key just before it louder still. One position off in the block's start, in prompts or in
     single rows, and the result is another key's value."""
-    for cut in ((0, 0), (40, 21), (59, 39)):  # whole; cut inside a block; last rows one by one
+    for cut in ((0, 0), (40, 21), (59, 39), (60 - 1, 41 - 1), (40, 40)):
+        # whole; cut inside a block; the last rows; single rows at a block's last and first place
         got, want = _attention_case(dtype, H=4, G=2, dim=8, vdim=8, chunk=20, page=16, turned=4,
                                     lengths=(60, 41), cut=cut, normed=False, loud=True, seed=9)
         # (a fault here moves the result by the size of a value; a score of 20 rounded to
