@@ -24,7 +24,7 @@ namespace ayk {
 
 constexpr int MOE_TM = 32;   // pairs per tile
 constexpr int MOE_TN = 64;   // output columns per tile
-constexpr int MOE_TK = 32;   // k per turn
+constexpr int MOE_TK = 32;   // k per turn on the CUDA cores (the tensor-core tiles take 64)
 constexpr int MOE_MAX_EXPERTS = 1024;
 
 // ---------------------------------------------------------------------------------------------
@@ -124,6 +124,7 @@ template <typename T, int PHASE> struct TileAcc;
 
 // fp32: thread (ty, tx) of 16 x 16 owns rows 2 ty .. +1 and columns 4 tx .. +3
 template <int PHASE> struct TileAcc<float, PHASE> {
+  static constexpr int TK = MOE_TK;
   static constexpr int LDS = MOE_TK + 1;
   float acc[PHASE == 0 ? 2 : 1][2][4];
   __device__ __forceinline__ void zero() {
@@ -173,7 +174,8 @@ template <int PHASE> struct TileAcc<float, PHASE> {
 // accumulators per matrix. Shared rows are padded by 8 entries so that a fragment's eight
 // rows fall into different banks.
 template <int PHASE> struct TileAcc<__nv_bfloat16, PHASE> {
-  static constexpr int LDS = MOE_TK + 8;
+  static constexpr int TK = 64;
+  static constexpr int LDS = TK + 8;
   float acc[PHASE == 0 ? 2 : 1][2][4];
   __device__ __forceinline__ void zero() {
 #pragma unroll
@@ -200,7 +202,7 @@ template <int PHASE> struct TileAcc<__nv_bfloat16, PHASE> {
     const int g = lane >> 2, t = lane & 3;
     const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 16;
 #pragma unroll
-    for (int k0 = 0; k0 < MOE_TK; k0 += 16) {
+    for (int k0 = 0; k0 < TK; k0 += 16) {
       uint32_t a[4];
       a[0] = pair_at(As + (m0 + g) * LDS + k0 + 2 * t);
       a[1] = pair_at(As + (m0 + g + 8) * LDS + k0 + 2 * t);
@@ -236,12 +238,13 @@ __global__ void __launch_bounds__(256)
 moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
                 const int* __restrict__ sorted, const int* __restrict__ tile_expert, int top,
                 int K, int N, float limit, float alpha, T* __restrict__ y, int ld_y,
-                float* __restrict__ out, int ld_out) {
+                float* __restrict__ out, int ld_out, int wide) {
   using Acc = TileAcc<T, PHASE>;
-  constexpr int LDS = Acc::LDS;
+  constexpr int LDS = Acc::LDS, TK = Acc::TK;
+  constexpr bool BF16 = sizeof(T) == 2;
   __shared__ __align__(16) T As[MOE_TM * LDS];
   __shared__ __align__(16) T Bs[MOE_TN * LDS];
-  __shared__ __align__(16) T Bs2[PHASE == 0 ? MOE_TN * LDS : 1];
+  __shared__ __align__(16) T Bs2[PHASE == 0 ? MOE_TN * LDS : 8];
   __shared__ int pair_s[MOE_TM];
   pdl_launch_dependents();
   const int tile = blockIdx.x, n0 = blockIdx.y * MOE_TN, tid = threadIdx.x;
@@ -254,26 +257,65 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
   const T* w = weight + (size_t)e * (PHASE == 0 ? 2 : 1) * N * K;
   Acc acc;
   acc.zero();
-  for (int k0 = 0; k0 < K; k0 += MOE_TK) {
-    for (int idx = tid; idx < MOE_TM * MOE_TK; idx += 256) {
-      const int r = idx / MOE_TK, k = idx % MOE_TK;
-      const int pair = pair_s[r];
-      T v = T(0.f);
-      if (pair >= 0 && k0 + k < K) {
-        const size_t row = PHASE == 0 ? (size_t)(pair / top) : (size_t)tile * MOE_TM + r;
-        v = a[row * lda + k0 + k];
+  if (BF16 && wide) {
+    // 16-byte pieces: the tile's rows of 64 k are eight pieces each; a thread brings one
+    // piece of the pairs' rows and two of each weight tile, and the next turn's pieces are
+    // on their way while this turn's products run
+    const int pr = tid >> 3, pk = (tid & 7) * 8;  // piece: row pr (+32 for the second), k pk
+    const int pair = pair_s[pr];
+    const T* a_row = pair < 0 ? nullptr
+                              : a + (PHASE == 0 ? (size_t)(pair / top)
+                                                : (size_t)tile * MOE_TM + pr) * lda;
+    uint4 ra, rb[2], rb2[2];
+    auto fetch = [&](int k0) {
+      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+      const bool in_k = k0 + pk < K;  // (K is a multiple of 8: a piece is inside or outside)
+      ra = (a_row != nullptr && in_k) ? *reinterpret_cast<const uint4*>(a_row + k0 + pk) : zero;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = n0 + pr + 32 * i;
+        const bool in = in_k && r < N;
+        rb[i] = in ? *reinterpret_cast<const uint4*>(w + (size_t)r * K + k0 + pk) : zero;
+        if (PHASE == 0) {
+          rb2[i] = in ? *reinterpret_cast<const uint4*>(w + (size_t)(N + r) * K + k0 + pk) : zero;
+        }
       }
-      As[r * LDS + k] = v;
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += TK) {
+      *reinterpret_cast<uint4*>(As + pr * LDS + pk) = ra;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        *reinterpret_cast<uint4*>(Bs + (pr + 32 * i) * LDS + pk) = rb[i];
+        if (PHASE == 0) *reinterpret_cast<uint4*>(Bs2 + (pr + 32 * i) * LDS + pk) = rb2[i];
+      }
+      __syncthreads();
+      if (k0 + TK < K) fetch(k0 + TK);
+      acc.step(As, Bs, Bs2);
+      __syncthreads();
     }
-    for (int idx = tid; idx < MOE_TN * MOE_TK; idx += 256) {
-      const int r = idx / MOE_TK, k = idx % MOE_TK;
-      const bool in = n0 + r < N && k0 + k < K;
-      Bs[r * LDS + k] = in ? w[(size_t)(n0 + r) * K + k0 + k] : T(0.f);
-      if (PHASE == 0) Bs2[r * LDS + k] = in ? w[(size_t)(N + n0 + r) * K + k0 + k] : T(0.f);
+  } else {
+    for (int k0 = 0; k0 < K; k0 += TK) {
+      for (int idx = tid; idx < MOE_TM * TK; idx += 256) {
+        const int r = idx / TK, k = idx % TK;
+        const int pair = pair_s[r];
+        T v = T(0.f);
+        if (pair >= 0 && k0 + k < K) {
+          const size_t row = PHASE == 0 ? (size_t)(pair / top) : (size_t)tile * MOE_TM + r;
+          v = a[row * lda + k0 + k];
+        }
+        As[r * LDS + k] = v;
+      }
+      for (int idx = tid; idx < MOE_TN * TK; idx += 256) {
+        const int r = idx / TK, k = idx % TK;
+        const bool in = n0 + r < N && k0 + k < K;
+        Bs[r * LDS + k] = in ? w[(size_t)(n0 + r) * K + k0 + k] : T(0.f);
+        if (PHASE == 0) Bs2[r * LDS + k] = in ? w[(size_t)(N + n0 + r) * K + k0 + k] : T(0.f);
+      }
+      __syncthreads();
+      acc.step(As, Bs, Bs2);
+      __syncthreads();
     }
-    __syncthreads();
-    acc.step(As, Bs, Bs2);
-    __syncthreads();
   }
   acc.each([&](int r, int c, float first, float second) {
     const int pair = pair_s[r];
@@ -311,15 +353,22 @@ int moe_experts(const void* hidden, int ld_hidden, const void* w_in, const void*
                 const int* sorted, const int* tile_expert, int max_tiles, int top, int width,
                 int ff, float limit, float alpha, void* y, int ld_y, float* pair_out, int ld_out,
                 cudaStream_t stream) {
+  // 16-byte pieces when every row of every operand starts on a 16-byte boundary
+  const auto aligned = [](const void* p) { return ((uintptr_t)p % 16) == 0; };
+  const int wide_in = sizeof(T) == 2 && width % 8 == 0 && ld_hidden % 8 == 0 &&
+                      aligned(hidden) && aligned(w_in);
+  const int wide_out = sizeof(T) == 2 && ff % 8 == 0 && ld_y % 8 == 0 && aligned(y) &&
+                       aligned(w_out);
   const dim3 grid_in(max_tiles, (ff + MOE_TN - 1) / MOE_TN);
   int status = launch_kernel(moe_tile_kernel<T, 0>, grid_in, dim3(256), 0, stream, 1,
                              (const T*)hidden, ld_hidden, (const T*)w_in, sorted, tile_expert,
-                             top, width, ff, limit, alpha, (T*)y, ld_y, (float*)nullptr, 0);
+                             top, width, ff, limit, alpha, (T*)y, ld_y, (float*)nullptr, 0,
+                             wide_in);
   if (status != AYK_OK) return status;
   const dim3 grid_out(max_tiles, (width + MOE_TN - 1) / MOE_TN);
   return launch_kernel(moe_tile_kernel<T, 1>, grid_out, dim3(256), 0, stream, 1, (const T*)y,
                        ld_y, (const T*)w_out, sorted, tile_expert, top, ff, width, limit, alpha,
-                       (T*)nullptr, 0, pair_out, ld_out);
+                       (T*)nullptr, 0, pair_out, ld_out, wide_out);
 }
 
 }  // namespace ayk

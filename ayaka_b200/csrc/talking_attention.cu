@@ -190,7 +190,8 @@ talking_attention_kernel(const T* __restrict__ qmix, int ld_qmix, const T* __res
 // (mma.sync m16n8k16, fp32 accumulators, the mixed queries held in registers), an online
 // softmax in fp32, and the weighted sum of its key/value head's values. The weights enter
 // that product as two bfloat16 terms, w = hi + lo, so that they carry 16 bits of mantissa
-// instead of 8. Keys past the segment's last position are zero in shared memory.
+// instead of 8. Keys past the segment's last position are zero in shared memory. A tile's
+// copies are asynchronous and fill one of two stages while the other is multiplied.
 constexpr int MMA_HEADS = 8;
 constexpr int MMA_KEYS = 32;
 
@@ -223,8 +224,9 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix
   using bf16 = __nv_bfloat16;
   const int kn = G * dim, vn = G * vdim;
   const int ldk = kn + 8, ldv = vn + 8;  // rows padded: a fragment's rows in different banks
-  bf16* Ks = reinterpret_cast<bf16*>(mma_smem);
-  bf16* Vs = Ks + MMA_KEYS * ldk;
+  const int stage_elems = MMA_KEYS * (ldk + ldv);
+  bf16* stages = reinterpret_cast<bf16*>(mma_smem);           // two stages of keys, values
+  int* pages_s = reinterpret_cast<int*>(stages + 2 * stage_elems);  // a segment's pages
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * window_rows, nrows = min(window_rows, rows - row0);
@@ -257,6 +259,23 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int kvh = active ? h / (H / G) : 0;
   const bool wide = (dim % 8 == 0) && (vdim % 8 == 0);  // 16-byte copies
+  // A token's keys and values are kc + vc pieces of 16 bytes. A warp copies the keys
+  // warp, warp + 8, ... of a tile, a lane the pieces lane, lane + 32, ...: where a piece
+  // lies in a page and in a stage does not depend on the tile, so it is worked out once.
+  constexpr int MAX_PIECES = 6;  // (256 + 1024) / 8 / 32 rounded up, and one
+  const int kc = kn / 8, vc = vn / 8;
+  int piece_src[MAX_PIECES], piece_dst[MAX_PIECES];  // elements; src < 0: no such piece
+#pragma unroll
+  for (int i = 0; i < MAX_PIECES; ++i) {
+    const int c = lane + 32 * i;
+    const bool key = c < kc;
+    const int e = (key ? c : c - kc) * 8;
+    const int width = key ? dim : vdim, head = e / width, d = e % width;
+    // bit 30 of the source marks a value piece; the row of the page's slot is added later
+    piece_src[i] = c < kc + vc ? ((head * page_size) * width + d) | (key ? 0 : 1 << 30) : -1;
+    piece_dst[i] = key ? e : MMA_KEYS * ldk + e;
+  }
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
   int first = 0;
   while (first < nrows) {
@@ -274,24 +293,40 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix
       const int c0 = chunk > 0 ? pos_s[first] - pos_s[first] % chunk : 0;
       const int p_last = pos_s[last];
       const int* table = block_table + (size_t)b * ld_table;
-      for (int k0 = c0; k0 <= p_last; k0 += MMA_KEYS) {
-        // the tile's keys and values into shared memory, zeros past the last position
+      // the segment's pages, fetched side by side; then the tiles of 32 keys travel into
+      // two stages in turn (asynchronous 16-byte copies, zeros past the last position),
+      // the next tile while this one is multiplied
+      const int page0 = c0 / page_size, npages = p_last / page_size - page0 + 1;
+      for (int i = tid; i < npages; i += MMA_HEADS * 32) pages_s[i] = table[page0 + i];
+      __syncthreads();
+      const int tiles = (p_last - c0) / MMA_KEYS + 1;
+      auto issue = [&](int tile) {
+        bf16* Kd = stages + (tile & 1) * stage_elems;
+        bf16* Vd = Kd + MMA_KEYS * ldk;
+        const int k0 = c0 + tile * MMA_KEYS;
         if (wide) {
-          const int kc = kn / 8, vc = vn / 8;
-          for (int idx = tid; idx < MMA_KEYS * (kc + vc); idx += MMA_HEADS * 32) {
-            const int j = idx / (kc + vc), c = idx % (kc + vc);
-            const int at = k0 + j;
-            uint4 value = make_uint4(0u, 0u, 0u, 0u);
-            const bool key = c < kc;
-            const int e = (key ? c : c - kc) * 8;  // entry among the token's kn (vn)
-            if (at <= p_last) {
-              const int page = table[at / page_size], s = at % page_size;
-              const int width = key ? dim : vdim, head = e / width, d = e % width;
-              const bf16* src = (key ? k_pages : v_pages) +
-                                (((size_t)page * G + head) * page_size + s) * width + d;
-              value = *reinterpret_cast<const uint4*>(src);
+#pragma unroll
+          for (int jj = 0; jj < MMA_KEYS / MMA_HEADS; ++jj) {
+            const int j = warp + MMA_HEADS * jj, at = k0 + j;
+            const bool in = at <= p_last;
+            const int index = page_shift >= 0 ? at >> page_shift : at / page_size;
+            const int sl = at - index * page_size;
+            const size_t page = in ? pages_s[index - page0] : 0;
+            const bf16* k_row = k_pages + page * G * page_size * dim + (size_t)sl * dim;
+            const bf16* v_row = v_pages + page * G * page_size * vdim + (size_t)sl * vdim;
+            const int bytes = in ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+#pragma unroll
+            for (int i = 0; i < MAX_PIECES; ++i) {
+              if (piece_src[i] >= 0) {
+                const bool value = (piece_src[i] >> 30) & 1;
+                const bf16* src = (value ? v_row : k_row) + (piece_src[i] & ((1 << 30) - 1));
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(
+                    Kd + (value ? j * ldv : j * ldk) + piece_dst[i]);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst),
+                             "l"(src), "r"(bytes)
+                             : "memory");
+              }
             }
-            *reinterpret_cast<uint4*>((key ? Ks + j * ldk : Vs + j * ldv) + e) = value;
           }
         } else {
           for (int idx = tid; idx < MMA_KEYS * (kn + vn); idx += MMA_HEADS * 32) {
@@ -301,15 +336,28 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix
             const int e = key ? c : c - kn;
             bf16 value = __float2bfloat16_rn(0.f);
             if (at <= p_last) {
-              const int page = table[at / page_size], s = at % page_size;
+              const int page = pages_s[at / page_size - page0], sl = at % page_size;
               const int width = key ? dim : vdim, head = e / width, d = e % width;
-              value = (key ? k_pages : v_pages)[(((size_t)page * G + head) * page_size + s) *
+              value = (key ? k_pages : v_pages)[(((size_t)page * G + head) * page_size + sl) *
                                                     width + d];
             }
-            (key ? Ks + j * ldk : Vs + j * ldv)[e] = value;
+            (key ? Kd + j * ldk : Vd + j * ldv)[e] = value;
           }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      };
+      issue(0);
+      for (int tile = 0; tile < tiles; ++tile) {
+        const int k0 = c0 + tile * MMA_KEYS;
+        if (tile + 1 < tiles) {
+          issue(tile + 1);
+          asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
         __syncthreads();
+        const bf16* Ks = stages + (tile & 1) * stage_elems;
+        const bf16* Vs = Ks + MMA_KEYS * ldk;
         if (active) {
           float sc[MMA_KEYS / 8][4];
 #pragma unroll
@@ -339,21 +387,21 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix
               for (int i = 0; i < 2; ++i) {
                 const int at = k0 + n * 8 + 2 * t + i;
                 float& v = sc[n][2 * half + i];
-                v = at <= reach ? v : -INFINITY;
+                v = at <= reach ? v * 1.4426950408889634f : -INFINITY;  // (base 2 from here)
                 best = fmaxf(best, v);
               }
             }
             best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, 1));
             best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, 2));
             const float m_new = fmaxf(m_run[half], best);
-            alpha[half] = m_new == -INFINITY ? 1.f : expf(m_run[half] - m_new);
+            alpha[half] = m_new == -INFINITY ? 1.f : exp2f(m_run[half] - m_new);
             float sum = 0.f;
 #pragma unroll
             for (int n = 0; n < MMA_KEYS / 8; ++n) {
 #pragma unroll
               for (int i = 0; i < 2; ++i) {
                 float& v = sc[n][2 * half + i];
-                v = m_new == -INFINITY ? 0.f : expf(v - m_new);
+                v = m_new == -INFINITY ? 0.f : exp2f(v - m_new);
                 sum += v;
               }
             }
@@ -396,7 +444,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix
             }
           }
         }
-        __syncthreads();  // the tile is overwritten at the next turn
+        __syncthreads();  // the stage is filled again at the next turn
       }
     }
     first = last + 1;
@@ -520,9 +568,11 @@ AYK_API int ayk_talking_attention(const void* qmix, int ld_qmix, const void* k_p
   }
   cudaStream_t s = (cudaStream_t)stream;
   const int kn = G * dim;
-  const size_t mma_smem = (size_t)MMA_KEYS * (kn + 8 + G * vdim + 8) * sizeof(__nv_bfloat16);
+  const size_t mma_smem = 2 * (size_t)MMA_KEYS * (kn + 8 + G * vdim + 8) * sizeof(__nv_bfloat16) +
+                          ((size_t)reach / page_size + 2) * sizeof(int);
   if (type == 1 && window == 0 && window_rows >= 1 && window_rows <= 16 && kn % 16 == 0 &&
-      kn <= 256 && vdim % 8 == 0 && vdim <= 128 && mma_smem <= 160 * 1024 &&
+      kn <= 256 && vdim % 8 == 0 && vdim <= 128 && G * vdim <= 1024 &&
+      mma_smem <= 160 * 1024 &&
       ld_qmix % 2 == 0 && ld_out % 2 == 0 && ((uintptr_t)qmix | (uintptr_t)out) % 4 == 0 &&
       ((uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0) {
     const dim3 grid((rows + window_rows - 1) / window_rows, (H + MMA_HEADS - 1) / MMA_HEADS);
