@@ -22,7 +22,8 @@
 
 namespace ayk {
 
-constexpr int MOE_TM = 32;   // pairs per tile
+constexpr int MOE_TM = 32;   // pairs per tile: few rows, and float32
+constexpr int MOE_TM_WIDE = 128;  // pairs per tile of the tensor-core products of many rows
 constexpr int MOE_TN = 64;   // output columns per tile
 constexpr int MOE_TK = 32;   // k per turn on the CUDA cores (the tensor-core tiles take 64)
 constexpr int MOE_MAX_EXPERTS = 1024;
@@ -74,10 +75,10 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, int r
   for (int j = 32 + lane; j < top; j += 32) share[(size_t)row * top + j] /= total;
 }
 
-// One CTA. sorted: [max_tiles * MOE_TM] pair indices or -1; tile_expert: [max_tiles], -1 for a
+// One CTA. sorted: [max_tiles * tile_rows] pair indices or -1; tile_expert: [max_tiles], -1 for a
 // tile past the last.
 __global__ void __launch_bounds__(1024)
-moe_align_kernel(const int* __restrict__ chosen, int pairs, int E, int max_tiles,
+moe_align_kernel(const int* __restrict__ chosen, int pairs, int E, int max_tiles, int tile_rows,
                  int* __restrict__ sorted, int* __restrict__ tile_expert) {
   __shared__ int counts[MOE_MAX_EXPERTS];
   __shared__ int starts[MOE_MAX_EXPERTS];
@@ -90,13 +91,13 @@ moe_align_kernel(const int* __restrict__ chosen, int pairs, int E, int max_tiles
     const int e = chosen[p];
     if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
   }
-  for (int i = tid; i < max_tiles * MOE_TM; i += blockDim.x) sorted[i] = -1;
+  for (int i = tid; i < max_tiles * tile_rows; i += blockDim.x) sorted[i] = -1;
   __syncthreads();
   if (tid == 0) {
     int tile = 0;
     for (int e = 0; e < E; ++e) {
-      starts[e] = tile * MOE_TM;
-      const int tiles = (counts[e] + MOE_TM - 1) / MOE_TM;
+      starts[e] = tile * tile_rows;
+      const int tiles = (counts[e] + tile_rows - 1) / tile_rows;
       for (int t = 0; t < tiles && tile < max_tiles; ++t) tile_expert[tile++] = e;
       counts[e] = 0;  // now the cursor of the expert's stretch
     }
@@ -120,10 +121,10 @@ __device__ __forceinline__ float expert_unit(float g, float u, float limit, floa
   return g / (1.f + expf(-alpha * g)) * (u + 1.f);
 }
 
-template <typename T, int PHASE> struct TileAcc;
+template <typename T, int PHASE, int TM> struct TileAcc;
 
 // fp32: thread (ty, tx) of 16 x 16 owns rows 2 ty .. +1 and columns 4 tx .. +3
-template <int PHASE> struct TileAcc<float, PHASE> {
+template <int PHASE> struct TileAcc<float, PHASE, MOE_TM> {
   static constexpr int TK = MOE_TK;
   static constexpr int LDS = MOE_TK + 1;
   float acc[PHASE == 0 ? 2 : 1][2][4];
@@ -170,23 +171,29 @@ template <int PHASE> struct TileAcc<float, PHASE> {
   }
 };
 
-// bfloat16: eight warps as 2 (rows of 16) x 4 (columns of 16); a warp holds two m16n8
-// accumulators per matrix. Shared rows are padded by 8 entries so that a fragment's eight
-// rows fall into different banks.
-template <int PHASE> struct TileAcc<__nv_bfloat16, PHASE> {
+// bfloat16: eight warps as (TM / 16 MT) x the rest; a warp holds MT x NT m16n8 accumulators
+// per matrix (tiles of 32 pairs: 2 x 4 warps of 16 x 16; of 128 pairs: 4 x 2 warps of
+// 32 x 32, four times the products per turn and a quarter of the weights' re-reads). Shared
+// rows are padded by 8 entries so that the eight rows of an ldmatrix tile fall into
+// different banks.
+template <int PHASE, int TM> struct TileAcc<__nv_bfloat16, PHASE, TM> {
   static constexpr int TK = 64;
   static constexpr int LDS = TK + 8;
-  float acc[PHASE == 0 ? 2 : 1][2][4];
+  static constexpr int MT = TM >= 128 ? 2 : 1;    // m16 tiles of a warp
+  static constexpr int WARPS_M = TM / (16 * MT);  // warps down the rows
+  static constexpr int WARPS_N = 8 / WARPS_M;
+  static constexpr int NT = MOE_TN / (8 * WARPS_N);  // n8 tiles of a warp (2 or 4)
+  static constexpr int W = PHASE == 0 ? 2 : 1;
+  float acc[W][MT][NT][4];
   __device__ __forceinline__ void zero() {
 #pragma unroll
-    for (int w = 0; w < (PHASE == 0 ? 2 : 1); ++w)
+    for (int w = 0; w < W; ++w)
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
+      for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[w][i][j] = 0.f;
-  }
-  static __device__ __forceinline__ uint32_t pair_at(const __nv_bfloat16* p) {
-    return *reinterpret_cast<const uint32_t*>(p);
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[w][m][n][i] = 0.f;
   }
   static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4],
                                              uint32_t b0, uint32_t b1) {
@@ -196,25 +203,42 @@ template <int PHASE> struct TileAcc<__nv_bfloat16, PHASE> {
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
+  // four 8 x 8 tiles of 16-bit entries, one 16-byte row address per lane
+  static __device__ __forceinline__ void load_tiles(uint32_t (&r)[4], const __nv_bfloat16* p) {
+    const uint32_t address = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(address));
+  }
   __device__ __forceinline__ void step(const __nv_bfloat16* As, const __nv_bfloat16* Bs,
                                        const __nv_bfloat16* Bs2) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 16;
+    const int m0 = (warp / WARPS_N) * 16 * MT, n0 = (warp % WARPS_N) * 8 * NT;
+    // A: lanes 0-15 give rows 0-15 at k, lanes 16-31 the same rows at k + 8 (a0..a3);
+    // B (kept [n][k]): lanes 0-7 rows n.. at k, 8-15 the same at k + 8 (b0, b1 of eight
+    // columns), 16-31 likewise for the next eight
+    const __nv_bfloat16* a_at = As + (m0 + (lane & 15)) * LDS + (lane >> 4) * 8;
+    const int b_offset = (n0 + (lane >> 4) * 8 + (lane & 7)) * LDS + ((lane >> 3) & 1) * 8;
 #pragma unroll
     for (int k0 = 0; k0 < TK; k0 += 16) {
-      uint32_t a[4];
-      a[0] = pair_at(As + (m0 + g) * LDS + k0 + 2 * t);
-      a[1] = pair_at(As + (m0 + g + 8) * LDS + k0 + 2 * t);
-      a[2] = pair_at(As + (m0 + g) * LDS + k0 + 2 * t + 8);
-      a[3] = pair_at(As + (m0 + g + 8) * LDS + k0 + 2 * t + 8);
+      uint32_t a[MT][4], b[4];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const __nv_bfloat16* b = Bs + (n0 + 8 * j + g) * LDS + k0 + 2 * t;
-        mma(acc[0][j], a, pair_at(b), pair_at(b + 8));
+      for (int m = 0; m < MT; ++m) load_tiles(a[m], a_at + m * 16 * LDS + k0);
+#pragma unroll
+      for (int n = 0; n < NT; n += 2) {
+        load_tiles(b, Bs + b_offset + n * 8 * LDS + k0);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          mma(acc[0][m][n], a[m], b[0], b[1]);
+          mma(acc[0][m][n + 1], a[m], b[2], b[3]);
+        }
         if (PHASE == 0) {
-          const __nv_bfloat16* b2 = Bs2 + (n0 + 8 * j + g) * LDS + k0 + 2 * t;
-          mma(acc[PHASE == 0 ? 1 : 0][j], a, pair_at(b2), pair_at(b2 + 8));
+          load_tiles(b, Bs2 + b_offset + n * 8 * LDS + k0);
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            mma(acc[W - 1][m][n], a[m], b[0], b[1]);
+            mma(acc[W - 1][m][n + 1], a[m], b[2], b[3]);
+          }
         }
       }
     }
@@ -222,36 +246,38 @@ template <int PHASE> struct TileAcc<__nv_bfloat16, PHASE> {
   template <typename F> __device__ __forceinline__ void each(F f) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int m0 = (warp >> 2) * 16, n0 = (warp & 3) * 16;
+    const int m0 = (warp / WARPS_N) * 16 * MT, n0 = (warp % WARPS_N) * 8 * NT;
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int m = 0; m < MT; ++m)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        f(m0 + g + (i >> 1) * 8, n0 + 8 * j + 2 * t + (i & 1), acc[0][j][i],
-          acc[PHASE == 0 ? 1 : 0][j][i]);
-      }
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          f(m0 + 16 * m + g + (i >> 1) * 8, n0 + 8 * n + 2 * t + (i & 1), acc[0][m][n][i],
+            acc[W - 1][m][n][i]);
+        }
   }
 };
 
-template <typename T, int PHASE>
-__global__ void __launch_bounds__(256)
+template <typename T, int PHASE, int TM>
+__global__ void __launch_bounds__(256, 2)  // two CTAs an SM: one's copies under the other's products
 moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
                 const int* __restrict__ sorted, const int* __restrict__ tile_expert, int top,
                 int K, int N, float limit, float alpha, T* __restrict__ y, int ld_y,
                 float* __restrict__ out, int ld_out, int wide) {
-  using Acc = TileAcc<T, PHASE>;
+  using Acc = TileAcc<T, PHASE, TM>;
   constexpr int LDS = Acc::LDS, TK = Acc::TK;
   constexpr bool BF16 = sizeof(T) == 2;
-  __shared__ __align__(16) T As[MOE_TM * LDS];
+  __shared__ __align__(16) T As[TM * LDS];
   __shared__ __align__(16) T Bs[MOE_TN * LDS];
   __shared__ __align__(16) T Bs2[PHASE == 0 ? MOE_TN * LDS : 8];
-  __shared__ int pair_s[MOE_TM];
+  __shared__ int pair_s[TM];
   pdl_launch_dependents();
   const int tile = blockIdx.x, n0 = blockIdx.y * MOE_TN, tid = threadIdx.x;
   pdl_wait_for(a, sorted, tile_expert);
   const int e = tile_expert[tile];
   if (e < 0) return;
-  if (tid < MOE_TM) pair_s[tid] = sorted[tile * MOE_TM + tid];
+  if (tid < TM) pair_s[tid] = sorted[tile * TM + tid];
   __syncthreads();
   // an expert's matrices: PHASE 0 [2 N][K] (gate rows, then up rows), PHASE 1 [N][K]
   const T* w = weight + (size_t)e * (PHASE == 0 ? 2 : 1) * N * K;
@@ -261,16 +287,25 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
     // 16-byte pieces: the tile's rows of 64 k are eight pieces each; a thread brings one
     // piece of the pairs' rows and two of each weight tile, and the next turn's pieces are
     // on their way while this turn's products run
-    const int pr = tid >> 3, pk = (tid & 7) * 8;  // piece: row pr (+32 for the second), k pk
-    const int pair = pair_s[pr];
-    const T* a_row = pair < 0 ? nullptr
-                              : a + (PHASE == 0 ? (size_t)(pair / top)
-                                                : (size_t)tile * MOE_TM + pr) * lda;
-    uint4 ra, rb[2], rb2[2];
+    const int pr = tid >> 3, pk = (tid & 7) * 8;  // piece: row pr (+32, +64, ...), k pk
+    constexpr int AP = TM / 32;                   // pieces of the pairs' rows per thread
+    const T* a_row[AP];
+#pragma unroll
+    for (int i = 0; i < AP; ++i) {
+      const int pair = pair_s[pr + 32 * i];
+      a_row[i] = pair < 0 ? nullptr
+                          : a + (PHASE == 0 ? (size_t)(pair / top)
+                                            : (size_t)tile * TM + pr + 32 * i) * lda;
+    }
+    uint4 ra[AP], rb[2], rb2[2];
     auto fetch = [&](int k0) {
       const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
       const bool in_k = k0 + pk < K;  // (K is a multiple of 8: a piece is inside or outside)
-      ra = (a_row != nullptr && in_k) ? *reinterpret_cast<const uint4*>(a_row + k0 + pk) : zero;
+#pragma unroll
+      for (int i = 0; i < AP; ++i) {
+        ra[i] = (a_row[i] != nullptr && in_k)
+                    ? *reinterpret_cast<const uint4*>(a_row[i] + k0 + pk) : zero;
+      }
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         const int r = n0 + pr + 32 * i;
@@ -283,7 +318,10 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
     };
     fetch(0);
     for (int k0 = 0; k0 < K; k0 += TK) {
-      *reinterpret_cast<uint4*>(As + pr * LDS + pk) = ra;
+#pragma unroll
+      for (int i = 0; i < AP; ++i) {
+        *reinterpret_cast<uint4*>(As + (pr + 32 * i) * LDS + pk) = ra[i];
+      }
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         *reinterpret_cast<uint4*>(Bs + (pr + 32 * i) * LDS + pk) = rb[i];
@@ -296,12 +334,12 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
     }
   } else {
     for (int k0 = 0; k0 < K; k0 += TK) {
-      for (int idx = tid; idx < MOE_TM * TK; idx += 256) {
+      for (int idx = tid; idx < TM * TK; idx += 256) {
         const int r = idx / TK, k = idx % TK;
         const int pair = pair_s[r];
         T v = T(0.f);
         if (pair >= 0 && k0 + k < K) {
-          const size_t row = PHASE == 0 ? (size_t)(pair / top) : (size_t)tile * MOE_TM + r;
+          const size_t row = PHASE == 0 ? (size_t)(pair / top) : (size_t)tile * TM + r;
           v = a[row * lda + k0 + k];
         }
         As[r * LDS + k] = v;
@@ -321,7 +359,7 @@ moe_tile_kernel(const T* __restrict__ a, int lda, const T* __restrict__ weight,
     const int pair = pair_s[r];
     if (pair < 0 || n0 + c >= N) return;
     if (PHASE == 0) {
-      stf(y + ((size_t)tile * MOE_TM + r) * ld_y + n0 + c,
+      stf(y + ((size_t)tile * TM + r) * ld_y + n0 + c,
           expert_unit(first, second, limit, alpha));
     } else {
       out[(size_t)pair * ld_out + n0 + c] = first;
@@ -348,7 +386,7 @@ __global__ void moe_join_kernel(const float* __restrict__ pair_out, int ld, cons
   }
 }
 
-template <typename T>
+template <typename T, int TM>
 int moe_experts(const void* hidden, int ld_hidden, const void* w_in, const void* w_out,
                 const int* sorted, const int* tile_expert, int max_tiles, int top, int width,
                 int ff, float limit, float alpha, void* y, int ld_y, float* pair_out, int ld_out,
@@ -359,14 +397,23 @@ int moe_experts(const void* hidden, int ld_hidden, const void* w_in, const void*
                       aligned(hidden) && aligned(w_in);
   const int wide_out = sizeof(T) == 2 && ff % 8 == 0 && ld_y % 8 == 0 && aligned(y) &&
                        aligned(w_out);
+  // (room in shared memory for two CTAs an SM: the default split may leave less)
+  static const bool carved = [] {
+    cudaFuncSetAttribute(moe_tile_kernel<T, 0, TM>,
+                         cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(moe_tile_kernel<T, 1, TM>,
+                         cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    return true;
+  }();
+  (void)carved;
   const dim3 grid_in(max_tiles, (ff + MOE_TN - 1) / MOE_TN);
-  int status = launch_kernel(moe_tile_kernel<T, 0>, grid_in, dim3(256), 0, stream, 1,
+  int status = launch_kernel(moe_tile_kernel<T, 0, TM>, grid_in, dim3(256), 0, stream, 1,
                              (const T*)hidden, ld_hidden, (const T*)w_in, sorted, tile_expert,
                              top, width, ff, limit, alpha, (T*)y, ld_y, (float*)nullptr, 0,
                              wide_in);
   if (status != AYK_OK) return status;
   const dim3 grid_out(max_tiles, (width + MOE_TN - 1) / MOE_TN);
-  return launch_kernel(moe_tile_kernel<T, 1>, grid_out, dim3(256), 0, stream, 1, (const T*)y,
+  return launch_kernel(moe_tile_kernel<T, 1, TM>, grid_out, dim3(256), 0, stream, 1, (const T*)y,
                        ld_y, (const T*)w_out, sorted, tile_expert, top, ff, width, limit, alpha,
                        (T*)nullptr, 0, pair_out, ld_out, wide_out);
 }
@@ -376,6 +423,7 @@ int moe_experts(const void* hidden, int ld_hidden, const void* w_in, const void*
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 AYK_API int ayk_moe_tile_rows() { return ayk::MOE_TM; }
+AYK_API int ayk_moe_tile_rows_wide() { return ayk::MOE_TM_WIDE; }
 
 AYK_API int ayk_moe_route(const float* logits, int ld, int rows, int experts, int top,
                           int* chosen, float* share, void* stream) {
@@ -391,14 +439,14 @@ AYK_API int ayk_moe_route(const float* logits, int ld, int rows, int experts, in
                        (cudaStream_t)stream, 1, logits, ld, rows, experts, top, chosen, share);
 }
 
-// Three launches: align, the two grouped products. `sorted` holds max_tiles * tile rows ints,
-// `tile_expert` max_tiles, `y` max_tiles * tile rows rows of ff, `pair_out` rows * top rows
-// of width. type: 0 = float32, 1 = bfloat16.
+// Three launches: align, the two grouped products. `sorted` holds max_tiles * tile_rows ints,
+// `tile_expert` max_tiles, `y` max_tiles * tile_rows rows of ff, `pair_out` rows * top rows
+// of width. type: 0 = float32, 1 = bfloat16. tile_rows: 32, or 128 (bfloat16 only).
 AYK_API int ayk_moe_experts(const void* hidden, int ld_hidden, const void* w_in,
                             const void* w_out, const int* chosen, int rows, int experts, int top,
                             int width, int ff, float limit, float alpha, int* sorted,
-                            int* tile_expert, int max_tiles, void* y, int ld_y, float* pair_out,
-                            int ld_out, int type, void* stream) {
+                            int* tile_expert, int max_tiles, int tile_rows, void* y, int ld_y,
+                            float* pair_out, int ld_out, int type, void* stream) {
   using namespace ayk;
   if (rows == 0) return AYK_OK;
   const long long pairs = (long long)rows * top;
@@ -406,22 +454,29 @@ AYK_API int ayk_moe_experts(const void* hidden, int ld_hidden, const void* w_in,
       w_in == nullptr || w_out == nullptr || chosen == nullptr || sorted == nullptr ||
       tile_expert == nullptr || y == nullptr || pair_out == nullptr || ld_hidden < width ||
       ld_y < ff || ld_out < width || !(limit > 0.f) ||
-      (long long)max_tiles * MOE_TM < pairs + (long long)min(experts, (int)pairs) * (MOE_TM - 1)) {
+      (tile_rows != MOE_TM && !(tile_rows == MOE_TM_WIDE && type == 1)) ||
+      (long long)max_tiles * tile_rows <
+          pairs + (long long)min(experts, (int)pairs) * (tile_rows - 1)) {
     return AYK_BAD_ARGUMENT;
   }
   if (experts > MOE_MAX_EXPERTS || max_tiles > 2000000) return AYK_TOO_LARGE;
   cudaStream_t s = (cudaStream_t)stream;
   int status = launch_kernel(moe_align_kernel, dim3(1), dim3(1024), 0, s, 1, chosen, (int)pairs,
-                             experts, max_tiles, sorted, tile_expert);
+                             experts, max_tiles, tile_rows, sorted, tile_expert);
   if (status != AYK_OK) return status;
   if (type == 0) {
-    return moe_experts<float>(hidden, ld_hidden, w_in, w_out, sorted, tile_expert, max_tiles,
+    return moe_experts<float, MOE_TM>(hidden, ld_hidden, w_in, w_out, sorted, tile_expert, max_tiles,
                               top, width, ff, limit, alpha, y, ld_y, pair_out, ld_out, s);
   }
+  if (type == 1 && tile_rows == MOE_TM_WIDE) {
+    return moe_experts<__nv_bfloat16, MOE_TM_WIDE>(hidden, ld_hidden, w_in, w_out, sorted,
+                                                   tile_expert, max_tiles, top, width, ff, limit,
+                                                   alpha, y, ld_y, pair_out, ld_out, s);
+  }
   if (type == 1) {
-    return moe_experts<__nv_bfloat16>(hidden, ld_hidden, w_in, w_out, sorted, tile_expert,
-                                      max_tiles, top, width, ff, limit, alpha, y, ld_y, pair_out,
-                                      ld_out, s);
+    return moe_experts<__nv_bfloat16, MOE_TM>(hidden, ld_hidden, w_in, w_out, sorted,
+                                              tile_expert, max_tiles, top, width, ff, limit,
+                                              alpha, y, ld_y, pair_out, ld_out, s);
   }
   return AYK_BAD_ARGUMENT;
 }

@@ -112,22 +112,34 @@ struct Branches {
 __global__ void norm_sum_kernel(Branches in, int count, float eps, float factor,
                                 const float* __restrict__ scale, float* __restrict__ dst,
                                 int ld_dst, int width, int accumulate) {
-  __shared__ float scratch[33];
+  __shared__ float scratch[SUM_MAX_BRANCHES][32];
   pdl_launch_dependents();
-  const int r = blockIdx.x;
+  const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
   pdl_wait_for(dst);
+  // the branches' sums of squares side by side, through one exchange
   float inv[SUM_MAX_BRANCHES];
 #pragma unroll
   for (int b = 0; b < SUM_MAX_BRANCHES; ++b) {
-    inv[b] = 0.f;
+    float s = 0.f;
     if (b < count) {
       const float* src = in.x[b] + (size_t)r * in.ld[b];
-      float s = 0.f;
       for (int c = threadIdx.x; c < width; c += blockDim.x) {
         const float v = src[c];
         s += v * v;
       }
-      inv[b] = 1.f / sqrtf(block_sum(s, scratch) / (float)width + eps);
+      s = warp_sum(s);
+      if (lane == 0) scratch[b][warp] = s;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int b = 0; b < SUM_MAX_BRANCHES; ++b) {
+    inv[b] = 0.f;
+    if (b < count) {
+      float s = 0.f;
+      for (int w = 0; w < warps; ++w) s += scratch[b][w];
+      inv[b] = 1.f / sqrtf(s / (float)width + eps);
     }
   }
   float* to = dst + (size_t)r * ld_dst;

@@ -26,6 +26,25 @@ __device__ __forceinline__ void rope_fill_table(float* cos_s, float* sin_s, int 
   }
 }
 
+// The same table with fewer double-precision operations: the angle position * f is formed
+// in double precision and brought into [-pi, pi] there (two multiplications and a rounding),
+// its sine and cosine are then taken in single precision, whose error on so small an argument
+// is about 1e-7. For kernels on a decode step's chain, where the double-precision sincos
+// of the function above is most of the kernel's time.
+__device__ __forceinline__ void rope_fill_table_reduced(float* cos_s, float* sin_s, int position,
+                                                        const double* __restrict__ freq,
+                                                        int pairs) {
+  const double two_pi = 6.283185307179586476925287, inv_two_pi = 0.159154943091895335768884;
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const double angle = (double)position * freq[i];
+    const float reduced = (float)(angle - two_pi * rint(angle * inv_two_pi));
+    float s, c;
+    sincosf(reduced, &s, &c);
+    cos_s[i] = c;
+    sin_s[i] = s;
+  }
+}
+
 // indices of pair i's two members inside the rotated stretch of `dims` entries
 __device__ __forceinline__ void rope_members(int i, int dims, int layout, int& a, int& b) {
   if (layout == ROPE_NEIGHBOURS) {

@@ -42,11 +42,18 @@ talking_prepare_kernel(const float* __restrict__ proj, int ld_proj, int k_off, i
   float* ks = qs + H * dim;         // G * dim
   float* cos_s = ks + G * dim;      // ROPE_MAX_PAIRS
   float* sin_s = cos_s + ROPE_MAX_PAIRS;
+  float* mix_s = sin_s + ROPE_MAX_PAIRS;  // H * H: talk[h][a] * temp[a] * scale
   pdl_launch_dependents();
   const int row = blockIdx.x, tid = threadIdx.x;
   const int qn = H * dim, kn = G * dim, pairs = rot_dims / 2;
   const int position = positions[row];
-  rope_fill_table(cos_s, sin_s, position, freq, pairs);
+  // (weights and positions are not the kernel ahead's: all this runs under its tail)
+  rope_fill_table_reduced(cos_s, sin_s, position, freq, pairs);
+  for (int i = tid; i < H * H; i += TALK_THREADS) {
+    const int a = i % H;
+    const float t = talk != nullptr ? talk[i] : (a == i / H ? 1.f : 0.f);
+    mix_s[i] = t * (temp != nullptr ? temp[a] : 1.f) * scale;
+  }
   pdl_wait_for(proj);
   const float* src = proj + (size_t)row * ld_proj;
   float sq = 0.f, sk = 0.f;
@@ -60,12 +67,28 @@ talking_prepare_kernel(const float* __restrict__ proj, int ld_proj, int k_off, i
     ks[i] = v;
     sk += v * v;
   }
+  {
+    // both sums of squares through one exchange
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if ((tid & 31) == 0) {
+      scratch[tid >> 5] = sq;
+      scratch[8 + (tid >> 5)] = sk;
+    }
+    __syncthreads();
+    sq = sk = 0.f;
+#pragma unroll
+    for (int w = 0; w < TALK_THREADS / 32; ++w) {
+      sq += scratch[w];
+      sk += scratch[8 + w];
+    }
+  }
   if (q_weight != nullptr) {
-    const float inv = 1.f / sqrtf(block_sum(sq, scratch) / (float)qn + eps);
+    const float inv = 1.f / sqrtf(sq / (float)qn + eps);
     for (int i = tid; i < qn; i += TALK_THREADS) qs[i] = qs[i] * inv * q_weight[i];
   }
   if (k_weight != nullptr) {
-    const float inv = 1.f / sqrtf(block_sum(sk, scratch) / (float)kn + eps);
+    const float inv = 1.f / sqrtf(sk / (float)kn + eps);
     for (int i = tid; i < kn; i += TALK_THREADS) ks[i] = ks[i] * inv * k_weight[i];
   }
   __syncthreads();
@@ -82,15 +105,15 @@ talking_prepare_kernel(const float* __restrict__ proj, int ld_proj, int k_off, i
   __syncthreads();
   const int per = H / G;
   T* mixed = qmix + (size_t)row * ld_qmix;
-  for (int idx = tid; idx < H * kn; idx += TALK_THREADS) {
-    const int h = idx / kn, g = (idx % kn) / dim, d = idx % dim;
-    float sum = 0.f;
-    for (int a = g * per; a < (g + 1) * per; ++a) {
-      const float t = talk != nullptr ? talk[h * H + a] : (a == h ? 1.f : 0.f);
-      const float factor = t * (temp != nullptr ? temp[a] : 1.f) * scale;
-      sum = fmaf(factor, qs[a * dim + d], sum);
+  for (int j = tid; j < kn; j += TALK_THREADS) {  // entry j of the token-wide key: (g, d)
+    const int g = j / dim, d = j - g * dim;
+    const float* group = qs + (size_t)g * per * dim + d;  // the group's heads, dim apart
+    for (int h = 0; h < H; ++h) {
+      const float* factors = mix_s + h * H + g * per;
+      float sum = 0.f;
+      for (int a = 0; a < per; ++a) sum = fmaf(factors[a], group[a * dim], sum);
+      stf(mixed + (size_t)h * kn + j, sum);
     }
-    stf(mixed + idx, sum);
   }
   const int slot = slot_mapping != nullptr ? slot_mapping[row] : -1;
   if (slot >= 0 && k_pages != nullptr) {
@@ -479,7 +502,7 @@ int talking_prepare(const float* proj, int ld_proj, int k_off, int v_off, const 
                     const int* slot_mapping, void* k_pages, void* v_pages, int page_size,
                     void* qmix, int ld_qmix, int rows, int H, int G, int dim, int vdim,
                     cudaStream_t stream) {
-  const size_t smem = ((size_t)(H + G) * dim + 2 * ROPE_MAX_PAIRS) * sizeof(float);
+  const size_t smem = ((size_t)(H + G) * dim + 2 * ROPE_MAX_PAIRS + (size_t)H * H) * sizeof(float);
   if (smem > 160 * 1024) return AYK_TOO_LARGE;
   static const bool allowed = (allow_large_smem(talking_prepare_kernel<T>), true);
   (void)allowed;

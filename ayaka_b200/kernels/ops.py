@@ -46,6 +46,8 @@ __all__ = [
     "moe_join",
     "moe_max_tiles",
     "moe_route",
+    "moe_scratch",
+    "moe_tile_rows",
     "norm_sum",
     "rms_norm",
     "rope",
@@ -1316,15 +1318,32 @@ def scale_add(x: torch.Tensor, scale: torch.Tensor, dst: torch.Tensor, *, rows: 
 
 # ---- mixture of experts ---------------------------------------------------------------------
 
-#: pairs (row, chosen expert) per tile of the grouped products (``MOE_TM`` in ``csrc/moe.cu``)
+#: pairs (row, chosen expert) per tile of the grouped products (``MOE_TM`` in ``csrc/moe.cu``),
+#: and per tile of the bfloat16 products of steps with many rows (``MOE_TM_WIDE``)
 MOE_TILE_ROWS = 32
+MOE_TILE_ROWS_WIDE = 128
 
 
-def moe_max_tiles(rows: int, experts: int, top: int) -> int:
+def moe_max_tiles(rows: int, experts: int, top: int, tile_rows: int = MOE_TILE_ROWS) -> int:
     """Tiles the grouped products may need for ``rows`` rows: every expert's pairs are padded
     to whole tiles."""
     pairs = rows * top
-    return -(-(pairs + min(experts, pairs) * (MOE_TILE_ROWS - 1)) // MOE_TILE_ROWS)
+    return -(-(pairs + min(experts, pairs) * (tile_rows - 1)) // tile_rows)
+
+
+def moe_tile_rows(rows: int, experts: int, top: int, dtype: torch.dtype) -> int:
+    """Rows of a tile :func:`moe_experts` uses: the wide tile in bfloat16 once an expert gets
+    two narrow tiles' worth of pairs on average, else the narrow one."""
+    wide = dtype == torch.bfloat16 and rows * top >= 2 * MOE_TILE_ROWS * experts
+    return MOE_TILE_ROWS_WIDE if wide else MOE_TILE_ROWS
+
+
+def moe_scratch(rows: int, experts: int, top: int) -> tuple[int, int]:
+    """``(places, tiles)``: the most rows of ``sorted_pairs`` / ``inner`` and the most entries
+    of ``tile_expert`` any tile size needs for up to ``rows`` rows."""
+    sizes = (MOE_TILE_ROWS, MOE_TILE_ROWS_WIDE)
+    return (max(moe_max_tiles(rows, experts, top, t) * t for t in sizes),
+            max(moe_max_tiles(rows, experts, top, t) for t in sizes))
 
 
 def moe_route(logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor, *, top: int,
@@ -1357,7 +1376,7 @@ def moe_experts(hidden: torch.Tensor, w_in: torch.Tensor, w_out: torch.Tensor,
     ``y = g * sigmoid(alpha * g) * (u + 1)`` and ``pair_out[p] = W_down y`` (float32
     ``[N * top, width]``, unweighted). Scratch: ``sorted_pairs`` (int32, ``tiles * tile
     rows``), ``tile_expert`` (int32, ``tiles``) and ``inner`` (``[tiles * tile rows, ff]``,
-    compute dtype) for ``tiles = moe_max_tiles(rows, experts, top)``."""
+    compute dtype) sized by :func:`moe_scratch`."""
     op = "moe_experts"
     if _left_out and op in _left_out:
         return
@@ -1370,21 +1389,23 @@ def moe_experts(hidden: torch.Tensor, w_in: torch.Tensor, w_out: torch.Tensor,
     _need(op, "sorted_pairs", sorted_pairs, torch.int32, 1)
     _need(op, "tile_expert", tile_expert, torch.int32, 1)
     width, ff = hidden.shape[1], w_out.shape[1]
-    tiles = moe_max_tiles(rows, experts, top)
+    tile_rows = moe_tile_rows(rows, experts, top, hidden.dtype)
+    tiles = moe_max_tiles(rows, experts, top, tile_rows)
     if hidden.dtype not in _TYPE or not w_in.is_contiguous() or not w_out.is_contiguous() or \
             tuple(w_in.shape) != (experts * 2 * ff, width) or \
             tuple(w_out.shape) != (experts * width, ff) or inner.shape[1] != ff or \
             pair_out.shape[1] != width or rows > hidden.shape[0] or \
             chosen.shape[0] < rows * top or pair_out.shape[0] < rows * top or \
-            sorted_pairs.shape[0] < tiles * MOE_TILE_ROWS or tile_expert.shape[0] < tiles or \
-            inner.shape[0] < tiles * MOE_TILE_ROWS:
+            sorted_pairs.shape[0] < tiles * tile_rows or tile_expert.shape[0] < tiles or \
+            inner.shape[0] < tiles * tile_rows:
         raise BackendError(f"{op}: shapes do not fit")
     global _launches
     _launches += 2  # align and two products
     status = library("moe").ayk_moe_experts(
         _ptr(hidden), c_int(hidden.stride(0)), _ptr(w_in), _ptr(w_out), _ptr(chosen),
         c_int(rows), c_int(experts), c_int(top), c_int(width), c_int(ff), c_float(limit),
-        c_float(alpha), _ptr(sorted_pairs), _ptr(tile_expert), c_int(tiles), _ptr(inner),
+        c_float(alpha), _ptr(sorted_pairs), _ptr(tile_expert), c_int(tiles), c_int(tile_rows),
+        _ptr(inner),
         c_int(inner.stride(0)), _ptr(pair_out), c_int(pair_out.stride(0)),
         c_int(_TYPE[hidden.dtype]), _stream())
     check(status, op)

@@ -56,8 +56,7 @@ class MixtureOfExperts(FeedForward):
         n, work, top = step.num_rows, step.workspace, self.top
         # scratch for the largest step, so that its addresses never change
         most = work.max_rows
-        tiles = ops.moe_max_tiles(most, self.experts, top)
-        places = tiles * ops.MOE_TILE_ROWS
+        places, tiles = ops.moe_scratch(most, self.experts, top)
         logits = work.buffer("experts.logits", self.experts, torch.float32)
         chosen = work.buffer("experts.chosen", top, torch.int32).view(-1)
         share = work.buffer("experts.share", top, torch.float32).view(-1)

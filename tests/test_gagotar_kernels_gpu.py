@@ -272,10 +272,12 @@ def test_routing(experts, top):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows,width,experts,top,ff", [(1, 24, 5, 2, 12), (7, 40, 3, 1, 72),
-                                                       (150, 64, 3, 2, 32), (33, 128, 9, 9, 64)])
+                                                       (150, 64, 3, 2, 32), (33, 128, 9, 9, 64),
+                                                       (700, 72, 4, 2, 80), (90, 36, 2, 1, 44)])
 def test_the_experts_against_the_plain_mixture(dtype, rows, width, experts, top, ff):
     """Also more pairs per expert than a tile holds (150 rows, two of three experts each),
-    one chosen expert, and every expert chosen."""
+    one chosen expert, every expert chosen, the wide tiles of bfloat16 (from 64 pairs per
+    expert on), and widths that are no multiple of 8 (no 16-byte pieces)."""
     gen = torch.Generator().manual_seed(rows + experts)
     limit, alpha = 1.2, 1.702
 
@@ -295,8 +297,7 @@ def test_the_experts_against_the_plain_mixture(dtype, rows, width, experts, top,
     logits = (h @ w["router"].T).float().to(DEV)
     chosen = torch.empty(rows * top, dtype=torch.int32, device=DEV)
     share = torch.empty(rows * top, dtype=torch.float32, device=DEV)
-    tiles = ops.moe_max_tiles(rows, experts, top)
-    places = tiles * ops.MOE_TILE_ROWS
+    places, tiles = ops.moe_scratch(rows, experts, top)
     pair_out = torch.full((rows * top, width), float("nan"), dtype=torch.float32, device=DEV)
     ops.moe_route(logits, chosen, share, top=top, rows=rows)
     ops.moe_experts(h.to(**dev), w_in.to(**dev).contiguous(), w_out.to(**dev).contiguous(),
