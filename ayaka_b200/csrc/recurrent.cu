@@ -1,6 +1,6 @@
 // Layers with a running per-request state instead of cached keys: the short causal
-// convolution and the selective state-space recurrence of a Mamba-2 layer, and the matrix
-// memory of an mLSTM layer. A step brings each request's next rows (a prompt portion or one
+// convolution and the selective state-space recurrence of a Mamba-2 layer, the matrix
+// memory of an mLSTM layer, and a gated linear attention with a decay per key channel. A step brings each request's next rows (a prompt portion or one
 // token); the state a request left behind is read from its slot, carried over the rows in
 // order, and written back. Everything here is fp32.
 //
