@@ -285,7 +285,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix
   // A token's keys and values are kc + vc pieces of 16 bytes. A warp copies the keys
   // warp, warp + 8, ... of a tile, a lane the pieces lane, lane + 32, ...: where a piece
   // lies in a page and in a stage does not depend on the tile, so it is worked out once.
-  constexpr int MAX_PIECES = 6;  // (256 + 1024) / 8 / 32 rounded up, and one
+  constexpr int MAX_PIECES = 6;  // (512 + 1024) / 8 / 32
   const int kc = kn / 8, vc = vn / 8;
   int piece_src[MAX_PIECES], piece_dst[MAX_PIECES];  // elements; src < 0: no such piece
 #pragma unroll
@@ -492,7 +492,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix
 }
 
 template <typename K> inline void allow_large_smem(K kernel) {
-  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
 }
 
 template <typename T>
@@ -594,8 +594,8 @@ AYK_API int ayk_talking_attention(const void* qmix, int ld_qmix, const void* k_p
   const size_t mma_smem = 2 * (size_t)MMA_KEYS * (kn + 8 + G * vdim + 8) * sizeof(__nv_bfloat16) +
                           ((size_t)reach / page_size + 2) * sizeof(int);
   if (type == 1 && window == 0 && window_rows >= 1 && window_rows <= 16 && kn % 16 == 0 &&
-      kn <= 256 && vdim % 8 == 0 && vdim <= 128 && G * vdim <= 1024 &&
-      mma_smem <= 160 * 1024 &&
+      kn <= 512 && vdim % 8 == 0 && vdim <= 128 && G * vdim <= 1024 &&
+      mma_smem <= 200 * 1024 &&
       ld_qmix % 2 == 0 && ld_out % 2 == 0 && ((uintptr_t)qmix | (uintptr_t)out) % 4 == 0 &&
       ((uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0) {
     const dim3 grid((rows + window_rows - 1) / window_rows, (H + MMA_HEADS - 1) / MMA_HEADS);
@@ -612,8 +612,10 @@ AYK_API int ayk_talking_attention(const void* qmix, int ld_qmix, const void* k_p
   }
     if (kn <= 128 && vdim <= 64) AYK_TALK_MMA(8, 8);
     if (kn <= 128) AYK_TALK_MMA(8, 16);
-    if (vdim <= 64) AYK_TALK_MMA(16, 8);
-    AYK_TALK_MMA(16, 16);
+    if (kn <= 256 && vdim <= 64) AYK_TALK_MMA(16, 8);
+    if (kn <= 256) AYK_TALK_MMA(16, 16);
+    if (vdim <= 64) AYK_TALK_MMA(32, 8);
+    AYK_TALK_MMA(32, 16);
 #undef AYK_TALK_MMA
   }
   if (type == 0) {

@@ -40,7 +40,7 @@ def _attention_case(dtype, *, H, G, dim, vdim, chunk, page, turned, lengths, cut
     talk = torch.eye(H, dtype=torch.float64) + 0.4 * torch.randn(H, H, generator=gen,
                                                                  dtype=torch.float64)
     temp = 0.5 + torch.rand(H, generator=gen, dtype=torch.float64)
-    scale, eps = 0.37, 1e-5
+    scale, eps = 1.5 * dim ** -0.5, 1e-5  # (scores of a few units whatever the head size)
     starts = [sum(lengths[:b]) for b in range(len(lengths))]
     if loud:
         # in every block the first key (the last one a late query still sees) is loud, and
@@ -137,6 +137,10 @@ def _attention_case(dtype, *, H, G, dim, vdim, chunk, page, turned, lengths, cut
          cut=(69, 33)),
     dict(H=2, G=1, dim=64, vdim=72, chunk=16, page=8, turned=2, lengths=(40, 17, 16, 1),
          cut=(39, 16, 15, 0)),
+    # a token's key heads side by side are 512 and 384 entries
+    dict(H=4, G=4, dim=128, vdim=128, chunk=40, page=16, turned=64, lengths=(90, 41),
+         cut=(10, 40)),
+    dict(H=9, G=3, dim=128, vdim=48, chunk=64, page=32, turned=128, lengths=(70,), cut=(5,)),
 ])
 def test_prepare_and_attention_over_scrambled_pages(dtype, case):
     got, want = _attention_case(dtype, normed=True, loud=False, seed=5, **case)
