@@ -73,9 +73,9 @@ class RotScaling:
     factor: float
     low: float
     high: float
-    original: int
+    original: float
 
-    def as_tuple(self) -> tuple[float, float, float, int]:
+    def as_tuple(self) -> tuple[float, float, float, float]:
         return (self.factor, self.low, self.high, self.original)
 
 
@@ -151,10 +151,11 @@ def _left(entry: Mapping[str, object], where: str) -> GagotarLeft:
         scaling = RotScaling(_number(raw["factor"], f"{where}.rot.scaling.factor"),
                              _number(raw["low"], f"{where}.rot.scaling.low"),
                              _number(raw["high"], f"{where}.rot.scaling.high"),
-                             _count(raw["original"], f"{where}.rot.scaling.original"))
-        if scaling.factor <= 0 or scaling.low <= 0 or scaling.high <= scaling.low:
+                             _number(raw["original"], f"{where}.rot.scaling.original"))
+        if scaling.factor <= 0 or scaling.low <= 0 or scaling.high <= scaling.low or \
+                scaling.original <= 0:
             raise ConfigError(f"{where}.rot.scaling", "INVALID_RANGE",
-                              "needs factor > 0 and 0 < low < high")
+                              "needs factor > 0, original > 0 and 0 < low < high")
     return GagotarLeft(heads, kv_heads, dim, _count(entry["vdim"], f"{where}.vdim"),
                        _number(entry["scale"], f"{where}.scale"),
                        _count(mask["size"], f"{where}.mask.size"), rot_dims, base, scaling)

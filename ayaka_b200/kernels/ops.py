@@ -762,7 +762,7 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
 
 
 def rope_frequencies(dims: int, base: float, device: torch.device,
-                     scaling: tuple[float, float, float, int] | None = None) -> torch.Tensor:
+                     scaling: tuple[float, float, float, float] | None = None) -> torch.Tensor:
     """``f_i = base^(-2i / dims)`` for the ``dims / 2`` pairs, as float64 on ``device`` (the
     kernels form ``position * f_i`` and its sine and cosine in double precision).
 

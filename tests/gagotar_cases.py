@@ -69,6 +69,15 @@ TINY_C = model(320, 128, 2e-5, [
     layer(left(8, 4, 16, 32, 16), right(4, 16, 48, 6.0, 16), moe(2, 2, 128, 3.0)),
 ])
 
+#: nothing a multiple of 8 (the CUDA-core products and copies serve bfloat16 too), blocks of
+#: three positions and of one (a row sees itself only), a whole-number `original` as a float
+TINY_D = model(61, 52, 1e-5, [
+    layer(left(5, 5, 6, 10, 3, turned=4, scaling={"factor": 2.0, "low": 1.0, "high": 3.0,
+                                                  "original": 12.0}),
+          right(2, 5, 7, 3.0, 3), moe(2, 2, 9, 1.1)),
+    layer(left(3, 1, 10, 6, 1, base=20.0), right(3, 9, 5, 8.0, 4), moe(7, 3, 11, 2.0)),
+])
+
 LOUD = RandomInit(weight_std=0.16, scale_residual_projections=False, bias_std=0.1, norm_std=0.1)
 LOUD_WIDE = RandomInit(weight_std=0.1, scale_residual_projections=False, bias_std=0.1,
                        norm_std=0.1)

@@ -238,6 +238,30 @@ def logits(state: dict, config: dict, tokens: torch.Tensor) -> torch.Tensor:
     return linear(weighted_norm(x, state["final.norm"], eps), state["head"])
 
 
+def router_margins(state: dict, config: dict, tokens: torch.Tensor) -> torch.Tensor:
+    """Per position, the smallest over the layers of: the gap between the last chosen and the
+    first unchosen router logit, as a fraction of the layer's largest logit. Where the margin
+    is below the rounding of an engine's arithmetic the model is discontinuous: another
+    expert may rightly be chosen there, and the logits jump."""
+    eps = config["norm"]["eps"]
+    x = state["embed"][tokens]
+    margin = torch.full((tokens.shape[0],), float("inf"), dtype=x.dtype)
+    for index, entry in enumerate(config["layers"]):
+        w = sub(state, f"l{index}.")
+        mlp = entry.get("mlp")
+        if mlp is not None:
+            h = weighted_norm(x, w["norm1"], eps)
+            mid = x + w["ls1"] * side_by_side(h, sub(w, "mix."), entry["mixer"], eps)
+            z = linear(weighted_norm(mid, w["norm2"], eps), w["mlp.router"])
+            top = mlp["router"]["top"]
+            if top < z.shape[1]:
+                ordered, _ = torch.sort(z, dim=-1, descending=True)
+                margin = torch.minimum(margin, (ordered[:, top - 1] - ordered[:, top])
+                                       / z.abs().max())
+        x = layer(x, w, entry, eps)
+    return margin
+
+
 def cast_state(state: dict, dtype: torch.dtype) -> dict:
     return {name: t.to(dtype) if t.is_floating_point() else t for name, t in state.items()}
 

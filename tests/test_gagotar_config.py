@@ -18,10 +18,10 @@ from ayaka_b200.models import build_model
 from ayaka_b200.models.gagotar import gagotar_model_spec, gagotar_weight_rules
 from ayaka_b200.parts.base import CacheNeed
 from ayaka_b200.weights.random_init import random_state
-from gagotar_cases import LOUD, TINY_A, TINY_B, TINY_C
+from gagotar_cases import LOUD, TINY_A, TINY_B, TINY_C, TINY_D
 
 
-@pytest.mark.parametrize("config", [TINY_A, TINY_B, TINY_C])
+@pytest.mark.parametrize("config", [TINY_A, TINY_B, TINY_C, TINY_D])
 def test_configuration_round_trip(config):
     parsed = GagotarConfig.from_json_dict(config)
     again = GagotarConfig.from_json_dict(parsed.to_json_dict())
@@ -76,7 +76,7 @@ def test_the_decay_rank_comes_from_the_stored_tensor_when_no_key_gives_it():
     assert model.blocks[1].mixer.sides[1].decay_rank == 3
 
 
-@pytest.mark.parametrize("config", [TINY_A, TINY_B, TINY_C])
+@pytest.mark.parametrize("config", [TINY_A, TINY_B, TINY_C, TINY_D])
 def test_every_stored_tensor_has_a_rule_and_every_parameter_is_covered(config):
     from ayaka_b200.weights.loader import TensorSource, load_into
 

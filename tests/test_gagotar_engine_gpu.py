@@ -13,11 +13,12 @@ import torch
 import engine_support as support
 import plain_gagotar as plain
 from cases import random_tokens
-from gagotar_cases import LOUD, LOUD_WIDE, TINY_A, TINY_B, TINY_C, plain_logits
+from gagotar_cases import LOUD, LOUD_WIDE, TINY_A, TINY_B, TINY_C, TINY_D, plain_logits
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = {"a": (TINY_A, LOUD), "b": (TINY_B, LOUD), "c": (TINY_C, LOUD_WIDE)}
+CONFIGS = {"a": (TINY_A, LOUD), "b": (TINY_B, LOUD), "c": (TINY_C, LOUD_WIDE),
+           "d": (TINY_D, LOUD)}
 #: lengths around the blocks (5, 7, 16, 20, 48) and the page (16) of the configurations
 LENGTHS = (1, 2, 41, 97, 16, 145)
 
@@ -33,8 +34,24 @@ def _model(tmp_path, name: str, dtype: str):
     return config, folder, state
 
 
+def _without_close_calls(got: dict, expected: dict, state: dict, config: dict,
+                         sequences: dict, below: float) -> dict:
+    """``got`` with the positions taken from ``expected`` at which some router of the plain
+    model chooses by less than ``below`` of its logits' size. There the model is
+    discontinuous: an engine that rounds to 8 bits rightly lands on another expert now and
+    then (these random routers have such a position in every few hundred), the logits jump,
+    and no comparison can rest on it. A fault of bookkeeping moves the positions around it
+    too, which stay in."""
+    wide = plain.cast_state(state, torch.float64)
+    out = {}
+    for rid, tokens in sequences.items():
+        close = plain.router_margins(wide, config, torch.tensor(tokens)) < below
+        out[rid] = torch.where(close[:, None], expected[rid], got[rid])
+    return out
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_the_four_ways_of_cutting_the_work_agree_with_the_plain_model(tmp_path, name, dtype):
     config, folder, state = _model(tmp_path, name, dtype)
     sequences = _sequences(config)
@@ -47,6 +64,8 @@ def test_the_four_ways_of_cutting_the_work_agree_with_the_plain_model(tmp_path, 
             ("mixed", support.schedule_mixed(sequences, pool_tokens=320), 21)):
         core = support.build_core(folder, dtype, num_blocks=blocks, max_running=4)
         got = support.replay(core, steps)
+        if dtype == "bfloat16":
+            got = _without_close_calls(got, expected, state, config, sequences, 1.5e-2)
         support.assert_logits_close(got, expected, dtype, f"gagotar-{name}/{label}")
         assert not core.manager.live_requests()
         del core
