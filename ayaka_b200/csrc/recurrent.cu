@@ -477,6 +477,7 @@ gla_scan_kernel(const float* __restrict__ proj, int ld_proj, int k_offset, int v
       a_s[i] = expf(log_sigmoid_f(a_s[i]) * inv_tau);
     }
     __syncthreads();
+#pragma unroll 4
     for (int i = 0; i < count; ++i) {
       const float vv = v_s[i * SCAN_COLS + col];
       const float* qi = q_s + (size_t)i * N;
