@@ -491,6 +491,244 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Steps of single rows on the tensor cores. With one query row per request, the rows of an
+// m16n8k16 tile are sixteen *heads* of that row: one warp scores a tile of 16 keys for all of
+// them at once, and the warps of a CTA share out the row's tiles (warp w takes tiles w,
+// w + W, ...), each with a running maximum and sum of its own; the shares are merged through
+// shared memory in warp order. Heads of different key/value heads want different values:
+// per key/value head the weights of the other heads' rows are zeroed and the product added
+// into the same accumulators. A CTA per (row, sixteen heads).
+constexpr int DEC_KEYS = 16;
+
+template <int KSTEPS, int VT>
+__global__ void __launch_bounds__(256)
+talking_decode_mma_kernel(const __nv_bfloat16* __restrict__ qmix, int ld_qmix,
+                          const __nv_bfloat16* __restrict__ k_pages,
+                          const __nv_bfloat16* __restrict__ v_pages,
+                          const int* __restrict__ block_table, int ld_table,
+                          const int* __restrict__ request_of_row,
+                          const int* __restrict__ positions, const float* __restrict__ gate,
+                          int ld_gate, __nv_bfloat16* __restrict__ out, int ld_out, int H, int G,
+                          int dim, int vdim, int page_size, int chunk, int max_pages) {
+  extern __shared__ __align__(16) unsigned char dec_smem[];
+  using bf16 = __nv_bfloat16;
+  const int kn = G * dim, vn = G * vdim;
+  const int ldk = kn + 8, ldv = vn + 8;
+  const int warps = blockDim.x >> 5;
+  const int tile_elems = DEC_KEYS * (ldk + ldv);
+  const int merge_floats = 16 * (8 * VT + 2);  // per warp: o [16][8 VT], maximum, sum
+  bf16* tiles = reinterpret_cast<bf16*>(dec_smem);
+  float* merge = reinterpret_cast<float*>(tiles + (size_t)warps * tile_elems);
+  int* pages_s = reinterpret_cast<int*>(merge + (size_t)warps * merge_floats);
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int row = blockIdx.x, h0 = blockIdx.y * 16, heads = min(16, H - h0);
+  const int b = request_of_row[row];
+  if (b < 0) {  // a row of padding
+    for (int i = tid; i < heads * vdim; i += blockDim.x) {
+      out[(size_t)row * ld_out + (size_t)h0 * vdim + i] = __float2bfloat16_rn(0.f);
+    }
+    return;
+  }
+  const int position = positions[row];
+  const int c0 = chunk > 0 ? position - position % chunk : 0;
+  const int page0 = c0 / page_size, npages = min(position / page_size - page0 + 1, max_pages);
+  const int* table = block_table + (size_t)b * ld_table;
+  pdl_wait_for(qmix, k_pages, v_pages, gate);
+  for (int i = tid; i < npages; i += blockDim.x) pages_s[i] = table[page0 + i];
+  // the sixteen heads' mixed queries as A fragments: rows g and g + 8 are heads
+  uint32_t qa[KSTEPS][4];
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = g + (i & 1) * 8, c = ks * 16 + 2 * t + (i >> 1) * 8;
+      qa[ks][i] = (r < heads && c < kn)
+                      ? *reinterpret_cast<const uint32_t*>(
+                            qmix + (size_t)row * ld_qmix + (size_t)(h0 + r) * kn + c)
+                      : 0u;
+    }
+  }
+  float o[VT][4];
+#pragma unroll
+  for (int v = 0; v < VT; ++v)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[v][i] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int per = H / G;
+  const int kv_of[2] = {(h0 + g) / per, (h0 + g + 8) / per};  // the rows' key/value heads
+  const int kv_first = h0 / per, kv_last = (h0 + heads - 1) / per;
+  const int kc = kn / 8, vc = vn / 8;
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+  // where a lane's 16-byte pieces of a token lie in a page and in the tile: worked out once
+  constexpr int DEC_PIECES = 6;  // (512 + 1024) / 8 / 32
+  int piece_src[DEC_PIECES], piece_dst[DEC_PIECES];  // elements; src < 0: no such piece
+#pragma unroll
+  for (int i = 0; i < DEC_PIECES; ++i) {
+    const int c = lane + 32 * i;
+    const bool key = c < kc;
+    const int e = (key ? c : c - kc) * 8;
+    const int width = key ? dim : vdim, head = e / width, d = e % width;
+    piece_src[i] = c < kc + vc ? ((head * page_size) * width + d) | (key ? 0 : 1 << 30) : -1;
+    piece_dst[i] = key ? e : DEC_KEYS * ldk + e;
+  }
+  bf16* Ks = tiles + (size_t)warp * tile_elems;
+  bf16* Vs = Ks + DEC_KEYS * ldk;
+  __syncthreads();
+  const int ntiles = (position - c0) / DEC_KEYS + 1;
+  for (int tile = warp; tile < ntiles; tile += warps) {
+    const int k0 = c0 + tile * DEC_KEYS;
+    __syncwarp();  // the warp has finished with the tile before
+#pragma unroll 4
+    for (int j = 0; j < DEC_KEYS; ++j) {
+      const int at = k0 + j;
+      const bool in = at <= position;
+      const int index = page_shift >= 0 ? at >> page_shift : at / page_size;
+      const int sl = at - index * page_size;
+      const size_t page = in ? pages_s[min(index - page0, npages - 1)] : 0;
+      const bf16* k_row = k_pages + page * G * page_size * dim + (size_t)sl * dim;
+      const bf16* v_row = v_pages + page * G * page_size * vdim + (size_t)sl * vdim;
+      const int bytes = in ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+#pragma unroll
+      for (int i = 0; i < DEC_PIECES; ++i) {
+        if (piece_src[i] >= 0) {
+          const bool value = (piece_src[i] >> 30) & 1;
+          const bf16* src = (value ? v_row : k_row) + (piece_src[i] & ((1 << 30) - 1));
+          const uint32_t dst = (uint32_t)__cvta_generic_to_shared(
+              Ks + (value ? j * ldv : j * ldk) + piece_dst[i]);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+                       "r"(bytes)
+                       : "memory");
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    float sc[DEC_KEYS / 8][4];
+#pragma unroll
+    for (int n = 0; n < DEC_KEYS / 8; ++n) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[n][i] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        if (ks * 16 < kn) {
+          const bf16* kb = Ks + (n * 8 + g) * ldk + ks * 16 + 2 * t;
+          mma_bf16(sc[n], qa[ks], *reinterpret_cast<const uint32_t*>(kb),
+                   *reinterpret_cast<const uint32_t*>(kb + 8));
+        }
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float best = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < DEC_KEYS / 8; ++n) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int at = k0 + n * 8 + 2 * t + i;
+          float& v = sc[n][2 * half + i];
+          v = at <= position ? v * 1.4426950408889634f : -INFINITY;  // (base 2 from here)
+          best = fmaxf(best, v);
+        }
+      }
+      best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, 1));
+      best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, 2));
+      const float m_new = fmaxf(m_run[half], best);  // (a tile holds a visible key: finite)
+      alpha[half] = exp2f(m_run[half] - m_new);
+      float sum = 0.f;
+#pragma unroll
+      for (int n = 0; n < DEC_KEYS / 8; ++n) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          float& v = sc[n][2 * half + i];
+          v = exp2f(v - m_new);
+          sum += v;
+        }
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l_run[half] = l_run[half] * alpha[half] + sum;
+      m_run[half] = m_new;
+    }
+#pragma unroll
+    for (int v = 0; v < VT; ++v) {
+      o[v][0] *= alpha[0];
+      o[v][1] *= alpha[0];
+      o[v][2] *= alpha[1];
+      o[v][3] *= alpha[1];
+    }
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float w0 = sc[i >> 1][2 * (i & 1)], w1 = sc[i >> 1][2 * (i & 1) + 1];
+      const float x0 = __bfloat162float(__float2bfloat16_rn(w0));
+      const float x1 = __bfloat162float(__float2bfloat16_rn(w1));
+      hi[i] = pack_bf16(x0, x1);
+      lo[i] = pack_bf16(w0 - x0, w1 - x1);
+    }
+    for (int kv = kv_first; kv <= kv_last; ++kv) {
+      // rows (heads) of other key/value heads add nothing: their weights are zeroed
+      uint32_t a_hi[4], a_lo[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool mine = kv_of[i & 1] == kv;
+        a_hi[i] = mine ? hi[i] : 0u;
+        a_lo[i] = mine ? lo[i] : 0u;
+      }
+#pragma unroll
+      for (int v = 0; v < VT; ++v) {
+        if (v * 8 < vdim) {
+          const int col = kv * vdim + v * 8 + g;
+          const unsigned short* vb =
+              reinterpret_cast<const unsigned short*>(Vs) + (2 * t) * ldv + col;
+          const uint32_t b0 = (uint32_t)vb[0] | ((uint32_t)vb[ldv] << 16);
+          const uint32_t b1 = (uint32_t)vb[8 * ldv] | ((uint32_t)vb[9 * ldv] << 16);
+          mma_bf16(o[v], a_hi, b0, b1);
+          mma_bf16(o[v], a_lo, b0, b1);
+        }
+      }
+    }
+  }
+  // every warp's share into its own rows of the merge area, then all threads merge
+  float* mine = merge + (size_t)warp * merge_floats;
+#pragma unroll
+  for (int v = 0; v < VT; ++v) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      mine[(g + (i >> 1) * 8) * (8 * VT + 2) + v * 8 + 2 * t + (i & 1)] = o[v][i];
+    }
+  }
+  if (t == 0) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      mine[(g + 8 * half) * (8 * VT + 2) + 8 * VT] = m_run[half];
+      mine[(g + 8 * half) * (8 * VT + 2) + 8 * VT + 1] = l_run[half];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < heads * vdim; idx += blockDim.x) {
+    const int r = idx / vdim, c = idx - r * vdim;
+    float best = -INFINITY;
+    for (int w = 0; w < warps; ++w) {
+      best = fmaxf(best, merge[(size_t)w * merge_floats + r * (8 * VT + 2) + 8 * VT]);
+    }
+    float total = 0.f, value = 0.f;
+    for (int w = 0; w < warps; ++w) {  // in warp order, whatever the batch
+      const float* part = merge + (size_t)w * merge_floats + r * (8 * VT + 2);
+      const float m = part[8 * VT];
+      const float weight = m == -INFINITY ? 0.f : exp2f(m - best);
+      total = fmaf(part[8 * VT + 1], weight, total);
+      value = fmaf(part[c], weight, value);
+    }
+    float factor = total > 0.f ? 1.f / total : 0.f;
+    if (gate != nullptr) factor /= 1.f + expf(-gate[(size_t)row * ld_gate + h0 + r]);
+    out[(size_t)row * ld_out + (size_t)(h0 + r) * vdim + c] = __float2bfloat16_rn(value * factor);
+  }
+}
+
 template <typename K> inline void allow_large_smem(K kernel) {
   cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
 }
@@ -598,6 +836,38 @@ AYK_API int ayk_talking_attention(const void* qmix, int ld_qmix, const void* k_p
       mma_smem <= 200 * 1024 &&
       ld_qmix % 2 == 0 && ld_out % 2 == 0 && ((uintptr_t)qmix | (uintptr_t)out) % 4 == 0 &&
       ((uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0) {
+    if (window_rows == 1) {
+      // steps of single rows: sixteen heads as a tile's rows, the warps share out the keys
+      const size_t per_warp = (size_t)DEC_KEYS * (kn + 8 + G * vdim + 8) * sizeof(__nv_bfloat16);
+      const int vt = vdim <= 64 ? 8 : 16;
+      const size_t merge_bytes = (size_t)16 * (8 * vt + 2) * sizeof(float);
+      const int max_pages = reach / page_size + 2;
+      const int tiles = (reach + DEC_KEYS - 1) / DEC_KEYS + 1;
+      int warps = 8;
+      while (warps > 1 && (warps * (per_warp + merge_bytes) > 180 * 1024 || warps >= 2 * tiles)) {
+        warps /= 2;
+      }
+      const size_t smem = warps * (per_warp + merge_bytes) + (size_t)max_pages * sizeof(int);
+      const dim3 dec_grid(rows, (H + 15) / 16);
+#define AYK_TALK_DEC(KS, VT)                                                                   \
+  {                                                                                            \
+    static const bool allowed = (allow_large_smem(talking_decode_mma_kernel<KS, VT>), true);   \
+    (void)allowed;                                                                             \
+    return launch_kernel(talking_decode_mma_kernel<KS, VT>, dec_grid, dim3(warps * 32), smem,  \
+                         s, 1, (const __nv_bfloat16*)qmix, ld_qmix,                            \
+                         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,         \
+                         block_table, ld_table, request_of_row, positions, gate, ld_gate,      \
+                         (__nv_bfloat16*)out, ld_out, H, G, dim, vdim, page_size, chunk,       \
+                         max_pages);                                                           \
+  }
+      if (smem <= 200 * 1024 && dim % 8 == 0) {
+        if (kn <= 256 && vdim <= 64) AYK_TALK_DEC(16, 8);
+        if (kn <= 256) AYK_TALK_DEC(16, 16);
+        if (vdim <= 64) AYK_TALK_DEC(32, 8);
+        AYK_TALK_DEC(32, 16);
+      }
+#undef AYK_TALK_DEC
+    }
     const dim3 grid((rows + window_rows - 1) / window_rows, (H + MMA_HEADS - 1) / MMA_HEADS);
 #define AYK_TALK_MMA(KS, VT)                                                                   \
   {                                                                                            \

@@ -137,6 +137,12 @@ def _attention_case(dtype, *, H, G, dim, vdim, chunk, page, turned, lengths, cut
          cut=(69, 33)),
     dict(H=2, G=1, dim=64, vdim=72, chunk=16, page=8, turned=2, lengths=(40, 17, 16, 1),
          cut=(39, 16, 15, 0)),
+    # steps of single rows: twenty heads (a CTA's sixteen and four more) over five key/value
+    # heads, the last key of a block, the first of the next, and a block's only key
+    dict(H=20, G=5, dim=16, vdim=16, chunk=50, page=16, turned=8, lengths=(75, 51, 50, 101),
+         cut=(74, 50, 49, 100)),
+    dict(H=3, G=1, dim=128, vdim=128, chunk=0 + 300, page=16, turned=128, lengths=(290, 17),
+         cut=(289, 16)),
     # a token's key heads side by side are 512 and 384 entries
     dict(H=4, G=4, dim=128, vdim=128, chunk=40, page=16, turned=64, lengths=(90, 41),
          cut=(10, 40)),
