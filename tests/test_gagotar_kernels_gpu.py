@@ -143,6 +143,10 @@ def _attention_case(dtype, *, H, G, dim, vdim, chunk, page, turned, lengths, cut
          cut=(74, 50, 49, 100)),
     dict(H=3, G=1, dim=128, vdim=128, chunk=0 + 300, page=16, turned=128, lengths=(290, 17),
          cut=(289, 16)),
+    # token-wide keys of 48 entries from heads of 12: the tensor-core kernel without its
+    # 16-byte copies, in portions and in single rows
+    dict(H=8, G=4, dim=12, vdim=8, chunk=10, page=8, turned=6, lengths=(45, 21), cut=(7, 3)),
+    dict(H=8, G=4, dim=12, vdim=8, chunk=10, page=8, turned=6, lengths=(45, 21), cut=(44, 20)),
     # a token's key heads side by side are 512 and 384 entries
     dict(H=4, G=4, dim=128, vdim=128, chunk=40, page=16, turned=64, lengths=(90, 41),
          cut=(10, 40)),
